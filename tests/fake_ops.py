@@ -33,14 +33,22 @@ def _normed_first(d, post_weight, post_eps, post_mult):
     return post_mult * post_weight * d * torch.rsqrt((d * d).mean(dim=-1, keepdim=True) + post_eps)
 
 
-def rmsnorm(x, delta, weight, eps, out, rows=None, status=None, post_weight=None, post_eps=0.0, post_mult=1.0):
+def rmsnorm(x, delta, weight, eps, out, rows=None, status=None, post_weight=None, post_eps=0.0, post_mult=1.0, groups=1,
+            x_scale=1.0, write_normed=False):
     idx = torch.arange(x.shape[0]) if rows is None else rows.long()
-    v = x[idx]
+    v = x[idx] * x_scale
     if delta is not None:
+        if delta.dim() == 3:                     # the unadded shares of a product
+            delta = delta.sum(dim=0)
         v = v + _normed_first(delta[idx].float(), post_weight, post_eps, post_mult)
+    if delta is not None or x_scale != 1.0:
         x[idx] = v
-    r = torch.rsqrt((v * v).mean(dim=-1, keepdim=True) + eps)
-    out.copy_((weight * v * r).to(out.dtype))
+    parts = v.view(v.shape[0], groups, -1)
+    y = weight * (parts * torch.rsqrt((parts * parts).mean(dim=-1, keepdim=True) + eps)).reshape(v.shape)
+    if out is not None:
+        out.copy_(y.to(out.dtype))
+    if write_normed:
+        x[idx] = y
 
 
 def silu_mul(gu, out, interleave=0):
@@ -268,7 +276,8 @@ def attention_prepare(y, q_col, k_col, v_col, positions, token_seq, frequencies,
 
 
 def attention_general(y, q_col, out, out_col, out_scale, k_cache, v_cache, positions, token_seq, block_table, heads, kv_heads,
-                      dim, v_dim, window, chunk, scale, status=None, keep_first=0, maps=1, lam=0.0, sub_eps=0.0):
+                      dim, v_dim, window, chunk, scale, status=None, keep_first=0, maps=1, lam=0.0, sub_eps=0.0, sinks=None,
+                      values_in_keys=False):
     T = y.shape[0]
     page_size = k_cache.shape[2]
     g = heads // kv_heads
@@ -286,10 +295,14 @@ def attention_general(y, q_col, out, out_col, out_scale, k_cache, v_cache, posit
         pages = block_table[s, (js // page_size)].long()
         assert bool((pages >= 0).all()), "attention reads a page that is not held"
         keys = k_cache[pages, :, js % page_size, :].float()
-        vals = v_cache[pages, :, js % page_size, :].float()
+        vals = keys[..., :v_dim] if values_in_keys else v_cache[pages, :, js % page_size, :].float()
         for h in range(heads):
             if maps == 1:
-                pr = torch.softmax((keys[:, h // g, :] @ q[t, h]) * scale, dim=0)
+                sc = (keys[:, h // g, :] @ q[t, h]) * scale
+                if sinks is not None:            # one more term in the denominator, without a value
+                    pr = torch.softmax(torch.cat([sc, sinks[h:h + 1].float()]), dim=0)[:-1]
+                else:
+                    pr = torch.softmax(sc, dim=0)
                 o = out_scale * (pr @ vals[:, h // g, :])
             else:
                 a = [torch.softmax((keys[:, (h // g) * 2 + m, :] @ q[t, 2 * h + m]) * scale, dim=0) @ vals[:, h // g, :] for m in range(2)]
@@ -319,9 +332,14 @@ def retention_carry(state, ends, starts, seq_row, seq_first, seq_count, seg_len,
         state[row] = S
 
 
-def retention_fix(y, q_col, positions, frequencies, starts, tiles, decay, o):
+def _silu(x):
+    return x / (1.0 + torch.exp(-x))
+
+
+def retention_fix(y, q_col, positions, frequencies, starts, tiles, decay, o, act=0):
     heads, dim, v_dim = starts.shape[1:]
-    q = _turned(y[:, q_col:q_col + heads * dim].float().view(-1, heads, dim).clone(), frequencies, positions)
+    q = y[:, q_col:q_col + heads * dim].float().view(-1, heads, dim).clone()
+    q = _turned(_silu(q) if act else q, frequencies, positions)
     for seg, begin, n, t0 in tiles.tolist():
         for t in range(begin, begin + n):
             add = torch.einsum("hdv,hd->hv", starts[seg], q[t]) * (decay ** (t - t0 + 1))[:, None]
@@ -329,9 +347,13 @@ def retention_fix(y, q_col, positions, frequencies, starts, tiles, decay, o):
 
 
 def retention_scan(y, q_col, k_col, v_col, decay, k_scale, frequencies, positions, state, cu_q, rows, o, heads, dim, v_dim,
-                   status=None, most_threads=0, ends=None):
+                   status=None, most_threads=0, ends=None, act=0):
     yf = y.float()
     T = y.shape[0]
+    if act:                                      # q, k and v pass through silu as they are read
+        yf = yf.clone()
+        for col, n in ((q_col, heads * dim), (k_col, heads * dim), (v_col, heads * v_dim)):
+            yf[:, col:col + n] = _silu(yf[:, col:col + n])
 
     def turn(x):
         if frequencies is not None and frequencies.numel():
@@ -357,25 +379,34 @@ def retention_scan(y, q_col, k_col, v_col, decay, k_scale, frequencies, position
             state[row] = S
 
 
-def route_experts(logits, top, act, inter, x=None, router=None):
+def _pick_weights(z, mode, scale):
+    if mode == 0:
+        return torch.softmax(z, dim=0)
+    s = torch.sigmoid(z)
+    return s / (s.sum() + 1e-20) * scale
+
+
+def route_experts(logits, top, act, inter, x=None, router=None, mode=0, scale=1.0):
     if logits is None:
         logits = x.float() @ router.float().t()
     T, n = logits.shape
     w = torch.zeros((T, n), dtype=torch.float32)
+    chosen = torch.zeros((T, n), dtype=torch.bool)
     for t in range(T):
         order = sorted(range(n), key=lambda e: (-float(logits[t, e]), e))[:top]
-        w[t, order] = torch.softmax(logits[t, order], dim=0)
+        w[t, order] = _pick_weights(logits[t, order], mode, scale)
+        chosen[t, order] = True
     scaled = act[:, :n * inter].float().view(T, n, inter) * w[:, :, None]
-    act[:, :n * inter] = torch.where(w[:, :, None] > 0, scaled, torch.zeros_like(scaled)).reshape(T, n * inter).to(act.dtype)
+    act[:, :n * inter] = torch.where(chosen[:, :, None], scaled, torch.zeros_like(scaled)).reshape(T, n * inter).to(act.dtype)
 
 
-def route_topk(logits, top, ids, weights, x=None, router=None):
+def route_topk(logits, top, ids, weights, x=None, router=None, mode=0, scale=1.0):
     if logits is None:
         logits = x.float() @ router.float().t()
     for t in range(logits.shape[0]):
         order = sorted(range(logits.shape[1]), key=lambda e: (-float(logits[t, e]), e))[:top]
         ids[t] = torch.tensor(order, dtype=torch.int32)
-        weights[t] = torch.softmax(logits[t, order], dim=0)
+        weights[t] = _pick_weights(logits[t, order], mode, scale)
 
 
 def expert_lists(ids, lists, counts):
@@ -402,3 +433,85 @@ def combine_picks(y, where, weights, shared_y, out):
     if shared_y is not None:
         acc = acc + shared_y.float()
     out.copy_(acc.to(out.dtype))
+
+
+# ---- the kernels of layers with a latent for each token ----
+
+
+def token_shift(x, mu, state, cu_q, rows, token_seq, out, status=None):
+    out.zero_()
+    for row, a, b in _sequences(cu_q, rows):
+        before = torch.cat([state[row][None], x[a:b - 1]], dim=0)
+        out[a:b] = (x[a:b] + (before - x[a:b]) * mu).to(out.dtype)
+        state[row] = x[b - 1]
+
+
+def _turn_pairs(v, positions, frequencies, mult):
+    """v [T, ..., n] float: the first 2 * len(frequencies) numbers in pairs (2i, 2i + 1) turned by position * frequencies[i]."""
+    if frequencies is None or not frequencies.numel():
+        return v
+    n = 2 * frequencies.numel()
+    ang = positions.float()[:, None] * frequencies.float()[None, :]
+    shape = [v.shape[0]] + [1] * (v.dim() - 2) + [frequencies.numel()]
+    c, s = (torch.cos(ang) * mult).reshape(shape), (torch.sin(ang) * mult).reshape(shape)
+    a, b = v[..., 0:n:2].clone(), v[..., 1:n:2].clone()
+    v = v.clone()
+    v[..., 0:n:2] = a * c - b * s
+    v[..., 1:n:2] = b * c + a * s
+    return v
+
+
+def latent_prepare(y, q_col, q_rank, kv_col, kv_rank, rot_dim, q_weight, k_weight, eps, frequencies, mult, positions, token_seq,
+                   block_table, cq, pages, store=True, status=None):
+    yf = y.float()
+    live = token_seq >= 0
+    norm = lambda v, w: v * torch.rsqrt((v * v).mean(dim=-1, keepdim=True) + eps) * w
+    cq[live, :q_rank] = norm(yf[:, q_col:q_col + q_rank], q_weight)[live].to(cq.dtype)
+    if not store:
+        return
+    c = norm(yf[:, kv_col:kv_col + kv_rank], k_weight)
+    r = _turn_pairs(yf[:, kv_col + kv_rank:kv_col + kv_rank + rot_dim], positions, frequencies, mult)
+    row = torch.cat([c, r], dim=-1).to(pages.dtype)
+    page_size = pages.shape[2]
+    for t in range(y.shape[0]):
+        if not bool(live[t]):
+            continue
+        p = int(positions[t])
+        page = int(block_table[int(token_seq[t]), p // page_size])
+        assert page >= 0, "a latent is stored into a page that is not held"
+        pages[page, 0, p % page_size, :] = row[t]
+
+
+def head_matmul(x, x_col, x_head, m, out, out_col, out_head, mode=0, tail=0, frequencies=None, mult=1.0, positions=None,
+                token_seq=None, gate=None, gate_col=0):
+    heads, inner, outer = m.shape
+    xf = x.float()
+    for h in range(heads):
+        a = xf[:, x_col + h * x_head:x_col + h * x_head + inner]
+        v = a @ m[h].float()
+        if mode == 2 and gate is not None:
+            v = v * torch.sigmoid(gate[:, gate_col + h * outer:gate_col + (h + 1) * outer].float())
+        out[:, out_col + h * out_head:out_col + h * out_head + outer] = v.to(out.dtype)
+        if mode == 1 and tail:
+            r = xf[:, x_col + h * x_head + inner:x_col + h * x_head + inner + tail]
+            turned = _turn_pairs(r, positions.clamp(min=0), frequencies, mult)
+            live = (token_seq >= 0)[:, None]
+            out[:, out_col + h * out_head + outer:out_col + h * out_head + outer + tail] = torch.where(live, turned, r).to(out.dtype)
+
+
+def xielu(z, out, ap, an):
+    v = z.float()
+    out.copy_(torch.where(v > 0, ap * v * v + 0.5 * v, an * (torch.expm1(v.clamp(max=0.0)) - v) + 0.5 * v).to(out.dtype))
+
+
+def gate_clamp(gu, out, interleave, alpha, limit, split, limit2):
+    inter = out.shape[1]
+    if interleave:
+        pairs = gu.view(gu.shape[0], inter // 8, 2, 8).float()
+        g, u = pairs[:, :, 0].reshape(-1, inter), pairs[:, :, 1].reshape(-1, inter)
+    else:
+        g, u = gu[:, :inter].float(), gu[:, inter:].float()
+    lim = torch.where(torch.arange(inter) >= split, torch.tensor(float(limit2)), torch.tensor(float(limit)))
+    g = torch.minimum(g, lim)
+    u = torch.maximum(torch.minimum(u, lim), -lim)
+    out.copy_((g * torch.sigmoid(alpha * g) * (u + 1.0)).to(out.dtype))

@@ -17,6 +17,7 @@ namespace vtb {
 
 namespace {
 constexpr int kMaxPerLane = 8;       // head sizes up to 256
+constexpr int kWidePerLane = 32;     // values of up to 1,024 numbers for the attention of one map
 constexpr int kPrepareWarps = 4;
 }
 
@@ -132,15 +133,20 @@ cudaError_t launch_attention_prepare(int dtype, void* y, int stride, int q_col, 
 // blocks that start at key 0.  MAPS 2: the head has two queries and its head of values two heads of keys; a lane forms
 // both scores of its key, each map keeps a maximum, a sum and a result of its own over the same values (read once),
 // and the end is o = a_1 - lam a_2, divided by its root mean square.
-template <typename T, bool Vec, int MAPS>
+// `sinks` [heads] (or null): one more term exp(sinks[h]) in the softmax's denominator, without a key or a value and not
+// scaled.  `v_stride`: elements from one value row to the next in `v_cache` (v_dim where the values have pages of their own;
+// the key's size where a value is the first v_dim numbers of its key's row and `v_cache` is `k_cache`).  PL: values of a
+// head that a lane holds (head sizes up to 32 PL); the queries lie in dynamic shared memory.
+template <typename T, bool Vec, int MAPS, int PL>
 __global__ void __launch_bounds__(128)
 attention_general_kernel(const T* __restrict__ y, int stride, int q_col, T* __restrict__ out, int out_stride, int out_col,
                          float out_scale, const T* __restrict__ k_cache, const T* __restrict__ v_cache,
                          const int* __restrict__ positions, const int* __restrict__ token_seq,
                          const int* __restrict__ block_table, int table_stride, int n_seqs, int n_pages, int n_tokens,
                          int heads, int kv_heads, int dim, int v_dim, int page_size, int window, int chunk, float scale,
-                         int* status, int keep_first, float lam, float sub_eps) {
-    __shared__ __align__(16) float qs[4][MAPS * 32 * kMaxPerLane];
+                         int* status, int keep_first, float lam, float sub_eps, const float* __restrict__ sinks, int v_stride) {
+    extern __shared__ __align__(16) float qs_all[];
+    constexpr int kMaxPerLane = PL;
     pdl_launch();
     pdl_wait();
     const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
@@ -160,9 +166,9 @@ attention_general_kernel(const T* __restrict__ y, int stride, int q_col, T* __re
     const int pos = positions[t];
     const int kvh = h / (heads / kv_heads);
     const int* table = block_table + (size_t)seq * table_stride;
-    float* q = qs[warp];
-    const T* qp = y + (size_t)t * stride + q_col + (size_t)h * MAPS * dim;
     const int dim_s = (dim + 3) & ~3;                              // a map's query starts on a 16-byte boundary
+    float* q = qs_all + warp * MAPS * dim_s;
+    const T* qp = y + (size_t)t * stride + q_col + (size_t)h * MAPS * dim;
     for (int i = lane; i < MAPS * dim; i += 32) q[(i / dim) * dim_s + i % dim] = to_float(qp[i]) * scale;
     __syncwarp();
 
@@ -234,7 +240,7 @@ attention_general_kernel(const T* __restrict__ y, int stride, int q_col, T* __re
 #pragma unroll
                 for (int m = 0; m < MAPS; ++m) pj[m] = __shfl_sync(0xffffffffu, p[m], jj);
                 const int aj = __shfl_sync(0xffffffffu, at_v, jj);
-                const T* vp = v_cache + (size_t)aj * v_dim;
+                const T* vp = v_cache + (size_t)aj * v_stride;
 #pragma unroll
                 for (int r = 0; r < kMaxPerLane; ++r) {
                     const int i = lane + 32 * r;
@@ -248,7 +254,13 @@ attention_general_kernel(const T* __restrict__ y, int stride, int q_col, T* __re
         }
     }
     if (MAPS == 1) {
-        const float inv = sum[0] > 0.f ? out_scale / sum[0] : 0.f;
+        float den = sum[0], keep = 1.f;
+        if (sinks != nullptr) {
+            const float sk = sinks[h], top = fmaxf(mx[0], sk);      // the sink may be the largest term
+            keep = expf(mx[0] - top);
+            den = sum[0] * keep + expf(sk - top);
+        }
+        const float inv = den > 0.f ? out_scale * keep / den : 0.f;
 #pragma unroll
         for (int r = 0; r < kMaxPerLane; ++r) {
             const int i = lane + 32 * r;
@@ -281,16 +293,19 @@ static cudaError_t launch_attention_general_t(const T* y, int stride, int q_col,
                                               const int* block_table, int table_stride, int n_seqs, int n_pages, int n_tokens,
                                               int heads, int kv_heads, int dim, int v_dim, int page_size, int window, int chunk,
                                               float scale, int* status, int keep_first, int maps, float lam, float sub_eps,
-                                              cudaStream_t stream) {
+                                              const float* sinks, int v_stride, cudaStream_t stream) {
     const long long pairs = (long long)n_tokens * heads;
     const int blocks = (int)((pairs + 3) / 4);
     // a key's row is read in 16-byte pieces where every row starts on such a boundary
     const bool vec = dim % 8 == 0 && (reinterpret_cast<uintptr_t>(k_cache) & 15) == 0;
-    auto kernel = maps == 2 ? (vec ? attention_general_kernel<T, true, 2> : attention_general_kernel<T, false, 2>)
-                            : (vec ? attention_general_kernel<T, true, 1> : attention_general_kernel<T, false, 1>);
-    return launch(kernel, blocks, 128, 0, stream, y, stride, q_col, out, out_stride, out_col, out_scale, k_cache, v_cache, positions,
+    const bool wide = v_dim > 32 * kMaxPerLane;                     // one map with values of up to 32 * kWidePerLane numbers
+    auto kernel = maps == 2 ? (vec ? attention_general_kernel<T, true, 2, kMaxPerLane> : attention_general_kernel<T, false, 2, kMaxPerLane>)
+                  : wide    ? (vec ? attention_general_kernel<T, true, 1, kWidePerLane> : attention_general_kernel<T, false, 1, kWidePerLane>)
+                            : (vec ? attention_general_kernel<T, true, 1, kMaxPerLane> : attention_general_kernel<T, false, 1, kMaxPerLane>);
+    const size_t bytes = (size_t)4 * maps * ((dim + 3) & ~3) * sizeof(float);
+    return launch(kernel, blocks, 128, bytes, stream, y, stride, q_col, out, out_stride, out_col, out_scale, k_cache, v_cache, positions,
                   token_seq, block_table, table_stride, n_seqs, n_pages, n_tokens, heads, kv_heads, dim, v_dim, page_size, window,
-                  chunk, scale, status, keep_first, lam, sub_eps);
+                  chunk, scale, status, keep_first, lam, sub_eps, sinks, v_stride > 0 ? v_stride : v_dim);
 }
 
 cudaError_t launch_attention_general(int dtype, const void* y, int stride, int q_col, void* out, int out_stride, int out_col,
@@ -298,18 +313,20 @@ cudaError_t launch_attention_general(int dtype, const void* y, int stride, int q
                                      const int* token_seq, const int* block_table, int table_stride, int n_seqs, int n_pages,
                                      int n_tokens, int heads, int kv_heads, int dim, int v_dim, int page_size, int window,
                                      int chunk, float scale, int* status, int keep_first, int maps, float lam, float sub_eps,
-                                     cudaStream_t stream) {
+                                     cudaStream_t stream, const float* sinks, int v_stride) {
     if (n_tokens == 0) return cudaSuccess;
-    if (dim > 32 * kMaxPerLane || v_dim > 32 * kMaxPerLane || (maps != 1 && maps != 2)) return cudaErrorInvalidValue;
+    // keys of any size up to what four queries take of shared memory; values up to 256 numbers (two maps) or 1,024 (one)
+    if (dim > 2048 || v_dim > 32 * (maps == 2 ? kMaxPerLane : kWidePerLane) || (maps != 1 && maps != 2)) return cudaErrorInvalidValue;
+    if (sinks != nullptr && maps != 1) return cudaErrorInvalidValue;
     if (dtype == kBF16)
         return launch_attention_general_t((const __nv_bfloat16*)y, stride, q_col, (__nv_bfloat16*)out, out_stride, out_col, out_scale,
                                           (const __nv_bfloat16*)k_cache, (const __nv_bfloat16*)v_cache, positions, token_seq,
                                           block_table, table_stride, n_seqs, n_pages, n_tokens, heads, kv_heads, dim, v_dim,
-                                          page_size, window, chunk, scale, status, keep_first, maps, lam, sub_eps, stream);
+                                          page_size, window, chunk, scale, status, keep_first, maps, lam, sub_eps, sinks, v_stride, stream);
     return launch_attention_general_t((const float*)y, stride, q_col, (float*)out, out_stride, out_col, out_scale, (const float*)k_cache,
                                       (const float*)v_cache, positions, token_seq, block_table, table_stride, n_seqs, n_pages,
                                       n_tokens, heads, kv_heads, dim, v_dim, page_size, window, chunk, scale, status, keep_first,
-                                      maps, lam, sub_eps, stream);
+                                      maps, lam, sub_eps, sinks, v_stride, stream);
 }
 
 }  // namespace vtb

@@ -65,14 +65,24 @@ void logits_scale_cap(Tensor& logits, double scale, double cap) {
                                               stream_of(logits)), "logits_scale_cap");
 }
 
-void norm_rows(bool center, Tensor& x, c10::optional<Tensor> delta, const Tensor& weight, double eps, Tensor& out,
+void norm_rows(bool center, Tensor& x, c10::optional<Tensor> delta, const Tensor& weight, double eps, c10::optional<Tensor> out_opt,
                c10::optional<Tensor> rows, c10::optional<Tensor> status, c10::optional<Tensor> post_weight, double post_eps,
-               double post_mult) {
-    check_f32(x, "x"); check_f32(weight, "weight"); check_cuda(out, "out");
-    TORCH_CHECK(x.dim() == 2 && out.dim() == 2, "rmsnorm: x and out must be 2-d");
+               double post_mult, int64_t groups = 1, double x_scale = 1.0, bool write_normed = false) {
+    check_f32(x, "x"); check_f32(weight, "weight");
+    TORCH_CHECK(x.dim() == 2, "rmsnorm: x must be 2-d");
     const int hidden = x.size(1);
     TORCH_CHECK(hidden % 8 == 0, "rmsnorm: hidden size ", hidden, " must be a multiple of 8");
+    TORCH_CHECK(groups >= 1 && hidden % groups == 0 && (hidden / groups) % 8 == 0, "rmsnorm: ", groups,
+                " groups must cut the hidden size ", hidden, " into equal parts of a multiple of 8 values");
+    TORCH_CHECK(!center || (groups == 1 && x_scale == 1.0 && !write_normed), "layernorm: no groups, scale of the stream or normed stream");
+    TORCH_CHECK(out_opt.has_value() || (write_normed && delta.has_value() && delta->dim() == 2),
+                "rmsnorm: without out the stream takes the normed row, and a delta tensor gives the dtype");
+    // without out (the normed row goes to the stream alone) the delta names the compute dtype
+    const Tensor& out = out_opt.has_value() ? *out_opt : *delta;
+    check_cuda(out, "out");
+    TORCH_CHECK(out.dim() == 2, "rmsnorm: out must be 2-d");
     TORCH_CHECK(weight.numel() == hidden && out.size(1) == hidden, "rmsnorm: weight and out must match hidden size");
+    TORCH_CHECK(!write_normed || !rows.has_value(), "rmsnorm: the normed row goes back to the stream for all rows or none");
     const int code = dtype_code(out, "out");
     const void* dp = nullptr;
     const float* pp = nullptr;
@@ -98,6 +108,7 @@ void norm_rows(bool center, Tensor& x, c10::optional<Tensor> delta, const Tensor
         n_rows = rows->numel();
     }
     TORCH_CHECK(out.size(0) == n_rows, "rmsnorm: out must have one row for each normed row");
+    TORCH_CHECK(out_opt.has_value() || (dp != nullptr), "rmsnorm: without out the delta must be a tensor");
     const float* pw = nullptr;
     if (post_weight.has_value()) {
         // the delta is normed (root mean square, this weight, post_mult) before it is added
@@ -107,17 +118,21 @@ void norm_rows(bool center, Tensor& x, c10::optional<Tensor> delta, const Tensor
         pw = post_weight->data_ptr<float>();
     }
     c10::cuda::CUDAGuard guard(x.device());
-    check_launch((center ? vtb::launch_layernorm : vtb::launch_rmsnorm)(code, x.data_ptr<float>(), dp, pp, n_parts,
-                                                                        weight.data_ptr<float>(), (float)eps, out.data_ptr(), rp,
-                                                                        n_rows, x.size(0), hidden, status_ptr(status), pw,
-                                                                        (float)post_eps, (float)post_mult,
-                                                                        stream_of(x)), center ? "layernorm" : "rmsnorm");
+    void* op = out_opt.has_value() ? out.data_ptr() : nullptr;
+    if (center)
+        check_launch(vtb::launch_layernorm(code, x.data_ptr<float>(), dp, pp, n_parts, weight.data_ptr<float>(), (float)eps, op, rp, n_rows,
+                                           x.size(0), hidden, status_ptr(status), pw, (float)post_eps, (float)post_mult, stream_of(x)),
+                     "layernorm");
+    else
+        check_launch(vtb::launch_rmsnorm(code, x.data_ptr<float>(), dp, pp, n_parts, weight.data_ptr<float>(), (float)eps, op, rp, n_rows,
+                                         x.size(0), hidden, status_ptr(status), pw, (float)post_eps, (float)post_mult, stream_of(x),
+                                         (int)groups, (float)x_scale, write_normed ? 1 : 0), "rmsnorm");
 }
 
-void rmsnorm(Tensor& x, c10::optional<Tensor> delta, const Tensor& weight, double eps, Tensor& out,
+void rmsnorm(Tensor& x, c10::optional<Tensor> delta, const Tensor& weight, double eps, c10::optional<Tensor> out,
              c10::optional<Tensor> rows, c10::optional<Tensor> status, c10::optional<Tensor> post_weight, double post_eps,
-             double post_mult) {
-    norm_rows(false, x, delta, weight, eps, out, rows, status, post_weight, post_eps, post_mult);
+             double post_mult, int64_t groups, double x_scale, bool write_normed) {
+    norm_rows(false, x, delta, weight, eps, out, rows, status, post_weight, post_eps, post_mult, groups, x_scale, write_normed);
 }
 
 void layernorm(Tensor& x, c10::optional<Tensor> delta, const Tensor& weight, double eps, Tensor& out,
@@ -259,24 +274,37 @@ void attention_prepare(Tensor& y, int64_t q_col, int64_t k_col, int64_t v_col, c
 void attention_general(const Tensor& y, int64_t q_col, Tensor& out, int64_t out_col, double out_scale, const Tensor& k_cache,
                        const Tensor& v_cache, const Tensor& positions, const Tensor& token_seq, const Tensor& block_table, int64_t heads,
                        int64_t kv_heads, int64_t dim, int64_t v_dim, int64_t window, int64_t chunk, double scale, c10::optional<Tensor> status,
-                       int64_t keep_first, int64_t maps, double lam, double sub_eps) {
+                       int64_t keep_first, int64_t maps, double lam, double sub_eps, c10::optional<Tensor> sinks, bool values_in_keys) {
     check_cuda(y, "y"); check_cuda(out, "out"); check_i32(positions, "positions"); check_i32(token_seq, "token_seq");
     TORCH_CHECK(maps == 1 || maps == 2, "attention_general: one map of queries and keys a head, or two");
+    const float* sp = nullptr;
+    if (sinks.has_value()) {
+        check_f32(*sinks, "sinks");
+        TORCH_CHECK(sinks->numel() == heads && maps == 1, "attention_general: one sink a head, with one map");
+        sp = sinks->data_ptr<float>();
+    }
     check_i32(block_table, "block_table");
     TORCH_CHECK(y.dim() == 2 && out.dim() == 2 && out.size(0) == y.size(0) && out.scalar_type() == y.scalar_type(),
                 "attention_general: y and out [tokens, .] of one dtype");
     TORCH_CHECK(positions.numel() == y.size(0) && token_seq.numel() == y.size(0), "attention_general: one position and sequence a token");
     TORCH_CHECK(block_table.dim() == 2 && heads % kv_heads == 0, "attention_general: block_table [sequences, stride]; heads a multiple of kv_heads");
     check_cols(y, q_col, heads * maps * dim, "attention_general (q)"); check_cols(out, out_col, heads * v_dim, "attention_general (out)");
-    check_pages(k_cache, v_cache, y, kv_heads * maps, dim, v_dim, kv_heads);
-    TORCH_CHECK(dim <= 256 && v_dim <= 256, "attention_general: head sizes up to 256");
+    if (values_in_keys) {
+        // a value is the first v_dim numbers of its key's row: one tensor of pages serves as both
+        TORCH_CHECK(maps == 1 && v_dim <= dim && v_cache.data_ptr() == k_cache.data_ptr(), "attention_general: values inside the keys' rows "
+                    "take one map, v_dim <= dim and the keys' pages as the values' pages");
+        check_pages(k_cache, k_cache, y, kv_heads, dim, dim, kv_heads);
+    } else {
+        check_pages(k_cache, v_cache, y, kv_heads * maps, dim, v_dim, kv_heads);
+    }
+    TORCH_CHECK(dim <= 2048 && v_dim <= (maps == 2 ? 256 : 1024), "attention_general: keys up to 2048 numbers, values up to 1024 (256 with two maps)");
     c10::cuda::CUDAGuard guard(y.device());
     check_launch(vtb::launch_attention_general(dtype_code(y, "y"), y.data_ptr(), y.size(1), q_col, out.data_ptr(), out.size(1), out_col,
                                                (float)out_scale, k_cache.data_ptr(), v_cache.data_ptr(), positions.data_ptr<int>(),
                                                token_seq.data_ptr<int>(), block_table.data_ptr<int>(), block_table.size(1),
                                                block_table.size(0), k_cache.size(0), y.size(0), heads, kv_heads, dim, v_dim, k_cache.size(2),
                                                window, chunk, (float)scale, status_ptr(status), keep_first, maps, (float)lam,
-                                               (float)sub_eps, stream_of(y)), "attention_general");
+                                               (float)sub_eps, stream_of(y), sp, values_in_keys ? (int)dim : 0), "attention_general");
 }
 
 void attention_diff(const Tensor& y, int64_t q_col, Tensor& out, int64_t out_col, double out_scale, const Tensor& k_cache,
@@ -317,7 +345,7 @@ void attention_diff(const Tensor& y, int64_t q_col, Tensor& out, int64_t out_col
 void retention_scan(const Tensor& y, int64_t q_col, int64_t k_col, int64_t v_col, const Tensor& decay, double k_scale,
                     c10::optional<Tensor> frequencies, const Tensor& positions, Tensor& state, const Tensor& cu_q, const Tensor& rows,
                     Tensor& o, int64_t heads, int64_t dim, int64_t v_dim, c10::optional<Tensor> status, int64_t most_threads,
-                    c10::optional<Tensor> ends) {
+                    c10::optional<Tensor> ends, int64_t act) {
     check_scan(y, state, cu_q, rows, o, heads, dim, v_dim, "retention_scan");
     float* ep = nullptr;
     int end_rows = 0;
@@ -344,7 +372,7 @@ void retention_scan(const Tensor& y, int64_t q_col, int64_t k_col, int64_t v_col
     check_launch(vtb::launch_retention_scan(dtype_code(y, "y"), y.data_ptr(), y.size(1), q_col, k_col, v_col, decay.data_ptr<float>(),
                                             (float)k_scale, fp, half, positions.data_ptr<int>(), state.data_ptr<float>(), state.size(0),
                                             cu_q.data_ptr<int>(), rows.data_ptr<int>(), rows.numel(), o.data_ptr<float>(), heads, dim,
-                                            v_dim, (int)most_threads, status_ptr(status), ep, end_rows, stream_of(y)), "retention_scan");
+                                            v_dim, (int)most_threads, status_ptr(status), ep, end_rows, stream_of(y), (int)act), "retention_scan");
 }
 
 void retention_carry(Tensor& state, const Tensor& ends, Tensor& starts, const Tensor& seq_row, const Tensor& seq_first,
@@ -364,7 +392,7 @@ void retention_carry(Tensor& state, const Tensor& ends, Tensor& starts, const Te
 }
 
 void retention_fix(const Tensor& y, int64_t q_col, const Tensor& positions, c10::optional<Tensor> frequencies, const Tensor& starts,
-                   const Tensor& tiles, const Tensor& decay, Tensor& o) {
+                   const Tensor& tiles, const Tensor& decay, Tensor& o, int64_t act) {
     check_cuda(y, "y"); check_i32(positions, "positions"); check_f32(starts, "starts"); check_i32(tiles, "tiles"); check_f32(decay, "decay");
     check_f32(o, "o");
     TORCH_CHECK(starts.dim() == 4 && tiles.dim() == 2 && tiles.size(1) == 4, "retention_fix: starts [n, heads, dim, v_dim], tiles [m, 4]");
@@ -383,7 +411,7 @@ void retention_fix(const Tensor& y, int64_t q_col, const Tensor& positions, c10:
     c10::cuda::CUDAGuard guard(y.device());
     check_launch(vtb::launch_retention_fix(dtype_code(y, "y"), y.data_ptr(), y.size(1), q_col, positions.data_ptr<int>(), fp, half,
                                            starts.data_ptr<float>(), tiles.data_ptr<int>(), tiles.size(0), decay.data_ptr<float>(),
-                                           o.data_ptr<float>(), heads, dim, v_dim, stream_of(y)), "retention_fix");
+                                           o.data_ptr<float>(), heads, dim, v_dim, stream_of(y), (int)act), "retention_fix");
 }
 
 // the router's logits as a tensor [tokens, experts], or the token's input x [tokens, width] and the router's matrix
@@ -412,7 +440,8 @@ RouterInput router_input(const c10::optional<Tensor>& logits, const c10::optiona
     return r;
 }
 
-void route_topk(c10::optional<Tensor> logits, int64_t top, Tensor& ids, Tensor& weights, c10::optional<Tensor> x, c10::optional<Tensor> router) {
+void route_topk(c10::optional<Tensor> logits, int64_t top, Tensor& ids, Tensor& weights, c10::optional<Tensor> x, c10::optional<Tensor> router,
+                int64_t mode, double scale) {
     check_i32(ids, "ids"); check_f32(weights, "weights");
     const RouterInput r = router_input(logits, x, router, "route_topk");
     TORCH_CHECK(ids.dim() == 2 && ids.size(0) == r.tokens && ids.size(1) == top && weights.sizes() == ids.sizes(),
@@ -420,7 +449,7 @@ void route_topk(c10::optional<Tensor> logits, int64_t top, Tensor& ids, Tensor& 
     TORCH_CHECK(r.experts <= 1024 && top >= 1 && top <= r.experts, "route_topk: 1 <= top <= experts <= 1024");
     c10::cuda::CUDAGuard guard(ids.device());
     check_launch(vtb::launch_route_topk(r.x_dtype, r.logits, r.x, r.router, r.width, r.tokens, r.experts, top, ids.data_ptr<int>(),
-                                        weights.data_ptr<float>(), stream_of(ids)), "route_topk");
+                                        weights.data_ptr<float>(), stream_of(ids), (int)mode, (float)scale), "route_topk");
 }
 
 void expert_lists(const Tensor& ids, Tensor& lists, Tensor& counts) {
@@ -459,7 +488,8 @@ void combine_picks(const Tensor& y, const Tensor& where, const Tensor& weights, 
                                            weights.size(1), out.size(0), sp, out.data_ptr(), stream_of(y)), "combine_picks");
 }
 
-void route_experts(c10::optional<Tensor> logits, int64_t top, Tensor& act, int64_t inter, c10::optional<Tensor> x, c10::optional<Tensor> router) {
+void route_experts(c10::optional<Tensor> logits, int64_t top, Tensor& act, int64_t inter, c10::optional<Tensor> x, c10::optional<Tensor> router,
+                   int64_t mode, double scale) {
     check_cuda(act, "act");
     const RouterInput r = router_input(logits, x, router, "route_experts");
     TORCH_CHECK(act.dim() == 2 && act.size(0) == r.tokens, "route_experts: act [tokens, .]");
@@ -468,9 +498,116 @@ void route_experts(c10::optional<Tensor> logits, int64_t top, Tensor& act, int64
     TORCH_CHECK(inter >= 0 && r.experts * inter <= act.size(1), "route_experts: experts * inter columns lie outside act");
     c10::cuda::CUDAGuard guard(act.device());
     check_launch(vtb::launch_route_experts(dtype_code(act, "act"), r.logits, r.x, r.router, r.width, r.tokens, r.experts, top, act.data_ptr(),
-                                           act.size(1), inter, stream_of(act)), "route_experts");
+                                           act.size(1), inter, stream_of(act), (int)mode, (float)scale), "route_experts");
 }
 
+
+
+// ---- layers with a latent for each token (latent.cu)
+
+void token_shift(const Tensor& x, const Tensor& mu, Tensor& state, const Tensor& cu_q, const Tensor& rows, const Tensor& token_seq,
+                 Tensor& out, c10::optional<Tensor> status) {
+    check_f32(x, "x"); check_f32(mu, "mu"); check_f32(state, "state"); check_i32(cu_q, "cu_q"); check_i32(rows, "rows");
+    check_i32(token_seq, "token_seq"); check_cuda(out, "out");
+    TORCH_CHECK(x.dim() == 2 && out.dim() == 2 && out.sizes() == x.sizes(), "token_shift: x and out [tokens, width]");
+    const int width = x.size(1);
+    TORCH_CHECK(mu.numel() == width && state.dim() == 2 && state.size(1) == width, "token_shift: mu [width], state [rows, width]");
+    TORCH_CHECK(cu_q.numel() == rows.numel() + 1 && token_seq.numel() == x.size(0), "token_shift: cu_q [sequences + 1], a sequence a token");
+    c10::cuda::CUDAGuard guard(x.device());
+    check_launch(vtb::launch_token_shift(dtype_code(out, "out"), x.data_ptr<float>(), mu.data_ptr<float>(), state.data_ptr<float>(),
+                                         state.size(0), cu_q.data_ptr<int>(), rows.data_ptr<int>(), token_seq.data_ptr<int>(), rows.numel(),
+                                         out.data_ptr(), x.size(0), width, status_ptr(status), stream_of(x)), "token_shift");
+}
+
+// (frequencies, half) of an optional tensor of rotation frequencies
+const float* frequencies_of(const c10::optional<Tensor>& frequencies, int& half) {
+    half = 0;
+    if (!frequencies.has_value()) return nullptr;
+    check_f32(*frequencies, "frequencies");
+    half = frequencies->numel();
+    return frequencies->data_ptr<float>();
+}
+
+void latent_prepare(const Tensor& y, int64_t q_col, int64_t q_rank, int64_t kv_col, int64_t kv_rank, int64_t rot_dim, const Tensor& q_weight,
+                    const Tensor& k_weight, double eps, c10::optional<Tensor> frequencies, double mult, const Tensor& positions,
+                    const Tensor& token_seq, const Tensor& block_table, Tensor& cq, Tensor& pages, bool store, c10::optional<Tensor> status) {
+    check_cuda(y, "y"); check_f32(q_weight, "q_weight"); check_f32(k_weight, "k_weight"); check_i32(positions, "positions");
+    check_i32(token_seq, "token_seq"); check_i32(block_table, "block_table"); check_cuda(cq, "cq"); check_cuda(pages, "pages");
+    TORCH_CHECK(y.dim() == 2 && cq.dim() == 2 && cq.size(0) == y.size(0) && cq.size(1) >= q_rank && cq.scalar_type() == y.scalar_type() &&
+                pages.scalar_type() == y.scalar_type(), "latent_prepare: y and cq [tokens, .] and the pages of one dtype");
+    check_cols(y, q_col, q_rank, "latent_prepare (queries' latent)"); check_cols(y, kv_col, kv_rank + rot_dim, "latent_prepare (keys' latent)");
+    TORCH_CHECK(pages.dim() == 4 && pages.size(1) == 1 && pages.size(3) == kv_rank + rot_dim, "latent_prepare: pages [pages, 1, page_size, kv_rank + rot_dim]");
+    TORCH_CHECK(q_weight.numel() == q_rank && k_weight.numel() == kv_rank, "latent_prepare: a weight for each latent");
+    TORCH_CHECK(positions.numel() == y.size(0) && token_seq.numel() == y.size(0) && block_table.dim() == 2, "latent_prepare: a position and "
+                "a sequence a token, block_table [sequences, stride]");
+    int half = 0;
+    const float* fp = frequencies_of(frequencies, half);
+    TORCH_CHECK(2 * half <= rot_dim, "latent_prepare: the rotation covers more than the rotated part");
+    c10::cuda::CUDAGuard guard(y.device());
+    check_launch(vtb::launch_latent_prepare(dtype_code(y, "y"), y.data_ptr(), y.size(1), q_col, q_rank, kv_col, kv_rank, rot_dim,
+                                            q_weight.data_ptr<float>(), k_weight.data_ptr<float>(), (float)eps, fp, half, (float)mult,
+                                            positions.data_ptr<int>(), token_seq.data_ptr<int>(), block_table.data_ptr<int>(),
+                                            block_table.size(1), block_table.size(0), pages.size(0), pages.size(2), cq.data_ptr(), cq.size(1),
+                                            pages.data_ptr(), store ? 1 : 0, y.size(0), status_ptr(status), stream_of(y)), "latent_prepare");
+}
+
+void head_matmul(const Tensor& x, int64_t x_col, int64_t x_head, const Tensor& m, Tensor& out, int64_t out_col, int64_t out_head, int64_t mode,
+                 int64_t tail, c10::optional<Tensor> frequencies, double mult, c10::optional<Tensor> positions,
+                 c10::optional<Tensor> token_seq, c10::optional<Tensor> gate, int64_t gate_col) {
+    check_cuda(x, "x"); check_cuda(m, "m"); check_cuda(out, "out");
+    TORCH_CHECK(x.dim() == 2 && out.dim() == 2 && m.dim() == 3 && out.size(0) == x.size(0) && out.scalar_type() == x.scalar_type(),
+                "head_matmul: x and out [tokens, .] of one dtype, m [heads, inner, outer]");
+    TORCH_CHECK(mode >= 0 && mode <= 2 && tail >= 0, "head_matmul: mode 0, 1 (a rotated tail) or 2 (a gate)");
+    const int heads = m.size(0), inner = m.size(1), outer = m.size(2);
+    TORCH_CHECK(inner <= 1536, "head_matmul: inner sizes up to 1536");
+    TORCH_CHECK(x_head >= inner + (mode == 1 ? tail : 0) && out_head >= outer + (mode == 1 ? tail : 0), "head_matmul: a head's inputs and "
+                "outputs overlap the next head's");
+    check_cols(x, x_col, (heads - 1) * x_head + inner + (mode == 1 ? tail : 0), "head_matmul (x)");
+    check_cols(out, out_col, (heads - 1) * out_head + outer + (mode == 1 ? tail : 0), "head_matmul (out)");
+    int half = 0;
+    const float* fp = frequencies_of(frequencies, half);
+    const int* pp = nullptr;
+    const int* tp = nullptr;
+    if (mode == 1) {
+        TORCH_CHECK(positions.has_value() && token_seq.has_value(), "head_matmul: a rotated tail needs positions and sequences");
+        check_i32(*positions, "positions"); check_i32(*token_seq, "token_seq");
+        TORCH_CHECK(positions->numel() == x.size(0) && token_seq->numel() == x.size(0) && 2 * half <= tail, "head_matmul: a position a token; "
+                    "the rotation within the tail");
+        pp = positions->data_ptr<int>();
+        tp = token_seq->data_ptr<int>();
+    }
+    const void* gp = nullptr;
+    int gate_stride = 0;
+    if (gate.has_value()) {
+        check_cuda(*gate, "gate");
+        TORCH_CHECK(mode == 2 && gate->dim() == 2 && gate->size(0) == x.size(0) && gate->scalar_type() == x.scalar_type(),
+                    "head_matmul: a gate [tokens, .] of x's dtype, with mode 2");
+        check_cols(*gate, gate_col, heads * outer, "head_matmul (gate)");
+        gp = gate->data_ptr();
+        gate_stride = gate->size(1);
+    }
+    c10::cuda::CUDAGuard guard(x.device());
+    check_launch(vtb::launch_head_matmul(dtype_code(x, "x"), dtype_code(m, "m"), x.data_ptr(), x.size(1), x_col, x_head, m.data_ptr(), heads,
+                                         inner, outer, out.data_ptr(), out.size(1), out_col, out_head, x.size(0), mode, tail, fp, half,
+                                         (float)mult, pp, tp, gp, gate_stride, gate_col, stream_of(x)), "head_matmul");
+}
+
+void xielu(const Tensor& z, Tensor& out, double ap, double an) {
+    check_cuda(z, "z"); check_cuda(out, "out");
+    TORCH_CHECK(out.sizes() == z.sizes() && out.scalar_type() == z.scalar_type(), "xielu: z and out of one shape and dtype");
+    c10::cuda::CUDAGuard guard(z.device());
+    check_launch(vtb::launch_xielu(dtype_code(z, "z"), z.data_ptr(), out.data_ptr(), z.numel(), (float)ap, (float)an, stream_of(z)), "xielu");
+}
+
+void gate_clamp(const Tensor& gu, Tensor& out, int64_t interleave, double alpha, double limit, int64_t split, double limit2) {
+    check_cuda(gu, "gu"); check_cuda(out, "out");
+    TORCH_CHECK(gu.dim() == 2 && out.dim() == 2 && gu.size(0) == out.size(0) && gu.size(1) == 2 * out.size(1) && out.size(1) % 8 == 0 &&
+                gu.scalar_type() == out.scalar_type(), "gate_clamp: gu [tokens, 2 n], out [tokens, n] of one dtype, n a multiple of 8");
+    TORCH_CHECK((interleave == 0 || interleave == 8) && split % 8 == 0, "gate_clamp: interleave 0 or 8; the second limit starts at a multiple of 8");
+    c10::cuda::CUDAGuard guard(gu.device());
+    check_launch(vtb::launch_gate_clamp(dtype_code(gu, "gu"), gu.data_ptr(), out.data_ptr(), gu.size(0), out.size(1), interleave, (float)alpha,
+                                        (float)limit, (int)split, (float)limit2, stream_of(gu)), "gate_clamp");
+}
 
 void scale_into(const Tensor& src, Tensor& dst, int64_t dst_col, double scale);
 
@@ -871,7 +1008,8 @@ PYBIND11_MODULE(TORCH_EXTENSION_NAME, m) {
     m.def("logits_scale_cap", &logits_scale_cap, py::arg("logits"), py::arg("scale"), py::arg("cap"));
     m.def("rmsnorm", &rmsnorm, py::arg("x"), py::arg("delta"), py::arg("weight"), py::arg("eps"), py::arg("out"),
           py::arg("rows") = py::none(), py::arg("status") = py::none(), py::arg("post_weight") = py::none(),
-          py::arg("post_eps") = 0.0, py::arg("post_mult") = 1.0);
+          py::arg("post_eps") = 0.0, py::arg("post_mult") = 1.0, py::arg("groups") = 1, py::arg("x_scale") = 1.0,
+          py::arg("write_normed") = false);
     m.def("layernorm", &layernorm, py::arg("x"), py::arg("delta"), py::arg("weight"), py::arg("eps"), py::arg("out"),
           py::arg("rows") = py::none(), py::arg("status") = py::none(), py::arg("post_weight") = py::none(),
           py::arg("post_eps") = 0.0, py::arg("post_mult") = 1.0);
@@ -893,20 +1031,34 @@ PYBIND11_MODULE(TORCH_EXTENSION_NAME, m) {
     m.def("attention_general", &attention_general, py::arg("y"), py::arg("q_col"), py::arg("out"), py::arg("out_col"), py::arg("out_scale"),
           py::arg("k_cache"), py::arg("v_cache"), py::arg("positions"), py::arg("token_seq"), py::arg("block_table"), py::arg("heads"),
           py::arg("kv_heads"), py::arg("dim"), py::arg("v_dim"), py::arg("window"), py::arg("chunk"), py::arg("scale"),
-          py::arg("status") = py::none(), py::arg("keep_first") = 0, py::arg("maps") = 1, py::arg("lam") = 0.0, py::arg("sub_eps") = 0.0);
+          py::arg("status") = py::none(), py::arg("keep_first") = 0, py::arg("maps") = 1, py::arg("lam") = 0.0, py::arg("sub_eps") = 0.0,
+          py::arg("sinks") = py::none(), py::arg("values_in_keys") = false);
     m.def("attention_diff", &attention_diff);
     m.def("attention_diff_supports", &vtb::attention_diff_supports);
     m.def("attention_diff_tile_rows", &vtb::attention_diff_tile_rows);
     m.def("retention_scan", &retention_scan, py::arg("y"), py::arg("q_col"), py::arg("k_col"), py::arg("v_col"), py::arg("decay"),
           py::arg("k_scale"), py::arg("frequencies"), py::arg("positions"), py::arg("state"), py::arg("cu_q"), py::arg("rows"), py::arg("o"),
           py::arg("heads"), py::arg("dim"), py::arg("v_dim"), py::arg("status") = py::none(), py::arg("most_threads") = 0,
-          py::arg("ends") = py::none());
+          py::arg("ends") = py::none(), py::arg("act") = 0);
     m.def("retention_carry", &retention_carry);
-    m.def("retention_fix", &retention_fix);
+    m.def("retention_fix", &retention_fix, py::arg("y"), py::arg("q_col"), py::arg("positions"), py::arg("frequencies"), py::arg("starts"),
+          py::arg("tiles"), py::arg("decay"), py::arg("o"), py::arg("act") = 0);
     m.def("route_experts", &route_experts, py::arg("logits"), py::arg("top"), py::arg("act"), py::arg("inter"), py::arg("x") = py::none(),
-          py::arg("router") = py::none());
+          py::arg("router") = py::none(), py::arg("mode") = 0, py::arg("scale") = 1.0);
     m.def("route_topk", &route_topk, py::arg("logits"), py::arg("top"), py::arg("ids"), py::arg("weights"), py::arg("x") = py::none(),
-          py::arg("router") = py::none());
+          py::arg("router") = py::none(), py::arg("mode") = 0, py::arg("scale") = 1.0);
+    m.def("token_shift", &token_shift, py::arg("x"), py::arg("mu"), py::arg("state"), py::arg("cu_q"), py::arg("rows"), py::arg("token_seq"),
+          py::arg("out"), py::arg("status") = py::none());
+    m.def("latent_prepare", &latent_prepare, py::arg("y"), py::arg("q_col"), py::arg("q_rank"), py::arg("kv_col"), py::arg("kv_rank"),
+          py::arg("rot_dim"), py::arg("q_weight"), py::arg("k_weight"), py::arg("eps"), py::arg("frequencies"), py::arg("mult"),
+          py::arg("positions"), py::arg("token_seq"), py::arg("block_table"), py::arg("cq"), py::arg("pages"), py::arg("store") = true,
+          py::arg("status") = py::none());
+    m.def("head_matmul", &head_matmul, py::arg("x"), py::arg("x_col"), py::arg("x_head"), py::arg("m"), py::arg("out"), py::arg("out_col"),
+          py::arg("out_head"), py::arg("mode") = 0, py::arg("tail") = 0, py::arg("frequencies") = py::none(), py::arg("mult") = 1.0,
+          py::arg("positions") = py::none(), py::arg("token_seq") = py::none(), py::arg("gate") = py::none(), py::arg("gate_col") = 0);
+    m.def("xielu", &xielu, py::arg("z"), py::arg("out"), py::arg("ap"), py::arg("an"));
+    m.def("gate_clamp", &gate_clamp, py::arg("gu"), py::arg("out"), py::arg("interleave"), py::arg("alpha"), py::arg("limit"),
+          py::arg("split"), py::arg("limit2"));
     m.def("expert_lists", &expert_lists);
     m.def("gather_picks", &gather_picks);
     m.def("combine_picks", &combine_picks);

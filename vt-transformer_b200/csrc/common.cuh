@@ -50,6 +50,13 @@ __device__ __forceinline__ int first_visible_key(int pos, int window, int chunk)
     return lo;
 }
 
+// The clamped gate of a feed-forward: g = min(gate, limit), u = clamp(up, -limit, limit), g * sigmoid(alpha g) * (u + 1).
+__device__ __forceinline__ float gate_clamp(float g, float u, float alpha, float limit) {
+    g = fminf(g, limit);
+    u = fminf(fmaxf(u, -limit), limit);
+    return g / (1.f + expf(-alpha * g)) * (u + 1.f);
+}
+
 __device__ __forceinline__ float warp_sum(float v) {
 #pragma unroll
     for (int o = 16; o > 0; o >>= 1) v += __shfl_xor_sync(0xffffffffu, v, o);

@@ -83,28 +83,36 @@ cudaError_t launch_logits_scale_cap(float* logits, long long n, float scale, flo
 // With `post_weight` the delta is itself normed before it is added: delta * rsqrt(mean(delta^2) + post_eps) * post_weight *
 // post_mult, in 32-bit (a layer that norms a sublayer's result before the residual sum): one more pass over the delta's row
 // for its sum of squares, whose order depends on hidden and the block size only.
+// Groups: a row of `row_size` values is `row_size / hidden` consecutive parts of `hidden` values, each normed by its own
+// root mean square (blockIdx.y is the part).  `x_scale` multiplies the stream before the delta is added (v = x_scale x + delta).
+// `write_normed`: the stream takes the normed row (in 32-bit) instead of the sum, for a layer whose norm comes after the sum;
+// `out` may then be null.
 template <typename T, bool Center>
 __global__ void rmsnorm_kernel(float* __restrict__ x, const T* __restrict__ delta, const float* __restrict__ parts,
                                int n_parts, const float* __restrict__ weight, float eps, T* __restrict__ out,
                                const int* __restrict__ rows, int n_tokens, int hidden, int* status,
-                               const float* __restrict__ post_weight, float post_eps, float post_mult) {
+                               const float* __restrict__ post_weight, float post_eps, float post_mult, int row_size,
+                               float x_scale, int write_normed) {
     __shared__ float scratch[32];
     pdl_launch();
     // the norm's weight and the list of rows are written by no kernel of the step: they are read before the wait
     const int r = blockIdx.x;
     const int t = rows ? rows[r] : r;
+    const int part0 = blockIdx.y * hidden;                   // where this block's part of the row begins
+    weight += part0;
+    if (post_weight != nullptr) post_weight += part0;
     float w_first[8];
     if ((int)threadIdx.x * 8 < hidden) Vec8<float>::load(weight + threadIdx.x * 8, w_first);
     pdl_wait();
-    T* o = out + (size_t)r * hidden;
+    T* o = out ? out + (size_t)r * row_size + part0 : nullptr;
     if (t < 0 || t >= n_tokens) {
         if (threadIdx.x == 0) set_status(status, kStatusBadRow, t);
         return;
     }
-    float* xr = x + (size_t)t * hidden;
-    const T* dr = delta ? delta + (size_t)t * hidden : nullptr;
-    const float* pr = parts ? parts + (size_t)t * hidden : nullptr;
-    const size_t stride = (size_t)n_tokens * hidden;
+    float* xr = x + (size_t)t * row_size + part0;
+    const T* dr = delta ? delta + (size_t)t * row_size + part0 : nullptr;
+    const float* pr = parts ? parts + (size_t)t * row_size + part0 : nullptr;
+    const size_t stride = (size_t)n_tokens * row_size;
     const int first = threadIdx.x * 8;
     // the delta (a tensor, or the shares in the order of their index) for the eight values at i
     auto delta_values = [&](int i, float (&d)[8]) {
@@ -137,6 +145,10 @@ __global__ void rmsnorm_kernel(float* __restrict__ x, const T* __restrict__ delt
     // v = x (+ delta) for the eight values at i
     auto row_values = [&](int i, float (&v)[8]) {
         Vec8<float>::load(xr + i, v);
+        if (x_scale != 1.f) {
+#pragma unroll
+            for (int j = 0; j < 8; ++j) v[j] *= x_scale;
+        }
         if (post_weight != nullptr && (dr || pr)) {
             float d[8], w[8];
             delta_values(i, d);
@@ -164,7 +176,7 @@ __global__ void rmsnorm_kernel(float* __restrict__ x, const T* __restrict__ delt
     for (int i = first; i < hidden; i += blockDim.x * 8) {
         float v[8];
         row_values(i, v);
-        if (dr || pr) Vec8<float>::store(xr + i, v);
+        if ((dr || pr || x_scale != 1.f) && !(once && write_normed)) Vec8<float>::store(xr + i, v);
 #pragma unroll
         for (int j = 0; j < 8; ++j) {
             ss += v[j] * v[j];
@@ -207,7 +219,8 @@ __global__ void rmsnorm_kernel(float* __restrict__ x, const T* __restrict__ delt
         }
 #pragma unroll
         for (int j = 0; j < 8; ++j) y[j] = w[j] * (v[j] - mean) * rs;
-        Vec8<T>::store(o + i, y);
+        if (o) Vec8<T>::store(o + i, y);
+        if (write_normed) Vec8<float>::store(xr + i, y);
     }
 }
 
@@ -215,22 +228,26 @@ template <bool Center>
 static cudaError_t launch_norm(int out_dtype, float* x, const void* delta, const float* parts, int n_parts,
                                const float* weight, float eps, void* out, const int* rows, int n_rows, int n_tokens,
                                int hidden, int* status, const float* post_weight, float post_eps, float post_mult,
-                               cudaStream_t stream) {
+                               cudaStream_t stream, int groups = 1, float x_scale = 1.f, int write_normed = 0) {
     if (delta != nullptr && parts != nullptr) return cudaErrorInvalidValue;
     if (n_rows == 0) return cudaSuccess;
-    int threads = min(512, max(32, ((hidden / 8 + 31) / 32) * 32));
+    if (groups < 1 || hidden % groups || (hidden / groups) % 8 || (out == nullptr && !write_normed)) return cudaErrorInvalidValue;
+    const int part = hidden / groups;                     // values that are normed together
+    int threads = min(512, max(32, ((part / 8 + 31) / 32) * 32));
+    const dim3 grid(n_rows, groups);
     if (out_dtype == kBF16)
-        return launch(rmsnorm_kernel<__nv_bfloat16, Center>, n_rows, threads, 0, stream, x, (const __nv_bfloat16*)delta, parts, n_parts, weight, eps,
-                      (__nv_bfloat16*)out, rows, n_tokens, hidden, status, post_weight, post_eps, post_mult);
-    return launch(rmsnorm_kernel<float, Center>, n_rows, threads, 0, stream, x, (const float*)delta, parts, n_parts, weight, eps, (float*)out, rows, n_tokens,
-                  hidden, status, post_weight, post_eps, post_mult);
+        return launch(rmsnorm_kernel<__nv_bfloat16, Center>, grid, threads, 0, stream, x, (const __nv_bfloat16*)delta, parts, n_parts, weight, eps,
+                      (__nv_bfloat16*)out, rows, n_tokens, part, status, post_weight, post_eps, post_mult, hidden, x_scale, write_normed);
+    return launch(rmsnorm_kernel<float, Center>, grid, threads, 0, stream, x, (const float*)delta, parts, n_parts, weight, eps, (float*)out, rows, n_tokens,
+                  part, status, post_weight, post_eps, post_mult, hidden, x_scale, write_normed);
 }
 
 cudaError_t launch_rmsnorm(int out_dtype, float* x, const void* delta, const float* parts, int n_parts,
                            const float* weight, float eps, void* out, const int* rows, int n_rows, int n_tokens,
-                           int hidden, int* status, const float* post_weight, float post_eps, float post_mult, cudaStream_t stream) {
+                           int hidden, int* status, const float* post_weight, float post_eps, float post_mult, cudaStream_t stream,
+                           int groups, float x_scale, int write_normed) {
     return launch_norm<false>(out_dtype, x, delta, parts, n_parts, weight, eps, out, rows, n_rows, n_tokens, hidden, status, post_weight,
-                       post_eps, post_mult, stream);
+                       post_eps, post_mult, stream, groups, x_scale, write_normed);
 }
 
 cudaError_t launch_layernorm(int out_dtype, float* x, const void* delta, const float* parts, int n_parts,

@@ -22,8 +22,10 @@ constexpr int kRouteThreads = 128;
 }
 
 // The `top` largest of z[0 .. experts) (the lower index among equals), by the first warp of the block: picked[k] and
-// picked_z[k] in falling order; z is used up.  Then w[e] = softmax over the picked logits (0 for the others) if w is given.
-__device__ __forceinline__ void pick_top(float* z, float* w, int* picked, float* picked_z, int experts, int top) {
+// picked_z[k] in falling order; z is used up.  Then w[e] = the pick's weight (0 for the others) if w is given: mode 0 the
+// softmax over the picked logits; mode 1 each pick's sigmoid(logit) over the picks' sum of them (+ 1e-20), times `scale`.
+__device__ __forceinline__ void pick_top(float* z, float* w, int* picked, float* picked_z, int experts, int top, int mode = 0,
+                                         float scale = 1.f) {
     const int lane = threadIdx.x & 31;
     if (threadIdx.x >= 32) return;
     for (int k = 0; k < top; ++k) {
@@ -46,7 +48,18 @@ __device__ __forceinline__ void pick_top(float* z, float* w, int* picked, float*
         }
         __syncwarp();
     }
-    if (lane == 0) {
+    if (lane == 0 && mode == 1) {
+        float sum = 0.f;
+        for (int k = 0; k < top; ++k) {
+            picked_z[k] = 1.f / (1.f + expf(-picked_z[k]));
+            sum += picked_z[k];
+        }
+        for (int k = 0; k < top; ++k) {
+            const float wk = picked_z[k] / (sum + 1e-20f) * scale;
+            picked_z[k] = wk;
+            if (w) w[picked[k]] = wk;
+        }
+    } else if (lane == 0) {
         const float mx = picked_z[0];                  // the first pick is the largest
         float sum = 0.f;
         for (int k = 0; k < top; ++k) sum += expf(picked_z[k] - mx);
@@ -88,7 +101,7 @@ __device__ __forceinline__ void router_logits(float* z, const float* __restrict_
 template <typename T>
 __global__ void __launch_bounds__(kRouteThreads)
 route_experts_kernel(const float* __restrict__ logits, const T* __restrict__ x, const float* __restrict__ router, int width,
-                     int experts, int top, T* __restrict__ act, int act_stride, int inter) {
+                     int experts, int top, T* __restrict__ act, int act_stride, int inter, int mode, float scale) {
     __shared__ float z[kMaxExperts];          // the logits; a picked one is taken out
     __shared__ float w[kMaxExperts];          // the experts' weights, zero for those not picked
     __shared__ float picked_z[kMaxExperts];
@@ -99,7 +112,7 @@ route_experts_kernel(const float* __restrict__ logits, const T* __restrict__ x, 
     for (int e = threadIdx.x; e < experts; e += blockDim.x) w[e] = 0.f;
     router_logits(z, logits, x, router, width, experts, t);
     __syncthreads();
-    pick_top(z, w, picked, picked_z, experts, top);
+    pick_top(z, w, picked, picked_z, experts, top, mode, scale);
     __syncthreads();
     T* row = act + (size_t)t * act_stride;
     if (inter % 8 == 0 && act_stride % 8 == 0 && (reinterpret_cast<uintptr_t>(act) & 15) == 0) {
@@ -129,7 +142,7 @@ route_experts_kernel(const float* __restrict__ logits, const T* __restrict__ x, 
 template <typename T>
 __global__ void __launch_bounds__(kRouteThreads)
 route_topk_kernel(const float* __restrict__ logits, const T* __restrict__ x, const float* __restrict__ router, int width, int experts,
-                  int top, int* __restrict__ ids, float* __restrict__ weights) {
+                  int top, int* __restrict__ ids, float* __restrict__ weights, int mode, float scale) {
     __shared__ float z[kMaxExperts];
     __shared__ float picked_z[kMaxExperts];
     __shared__ int picked[kMaxExperts];
@@ -138,7 +151,7 @@ route_topk_kernel(const float* __restrict__ logits, const T* __restrict__ x, con
     const int t = blockIdx.x;
     router_logits(z, logits, x, router, width, experts, t);
     __syncthreads();
-    pick_top(z, nullptr, picked, picked_z, experts, top);
+    pick_top(z, nullptr, picked, picked_z, experts, top, mode, scale);
     __syncthreads();
     for (int k = threadIdx.x; k < top; k += blockDim.x) {
         ids[(size_t)t * top + k] = picked[k];
@@ -231,14 +244,14 @@ combine_picks_kernel(const T* __restrict__ y, int width, const int* __restrict__
 }
 
 cudaError_t launch_route_topk(int x_dtype, const float* logits, const void* x, const float* router, int width, int n_tokens, int experts,
-                              int top, int* ids, float* weights, cudaStream_t stream) {
+                              int top, int* ids, float* weights, cudaStream_t stream, int mode, float scale) {
     if (n_tokens == 0) return cudaSuccess;
     if (experts < 1 || experts > kMaxExperts || top < 1 || top > experts || (x != nullptr && width % 8)) return cudaErrorInvalidValue;
     if (x_dtype == kBF16)
         return launch(route_topk_kernel<__nv_bfloat16>, n_tokens, kRouteThreads, 0, stream, logits, (const __nv_bfloat16*)x, router, width,
-                      experts, top, ids, weights);
+                      experts, top, ids, weights, mode, scale);
     return launch(route_topk_kernel<float>, n_tokens, kRouteThreads, 0, stream, logits, (const float*)x, router, width, experts, top, ids,
-                  weights);
+                  weights, mode, scale);
 }
 
 cudaError_t launch_expert_lists(const int* ids, int n_picks, int experts, int list_stride, int* lists, int* counts, cudaStream_t stream) {
@@ -269,14 +282,14 @@ cudaError_t launch_combine_picks(int dtype, const void* y, int width, const int*
 }
 
 cudaError_t launch_route_experts(int dtype, const float* logits, const void* x, const float* router, int width, int n_tokens, int experts,
-                                 int top, void* act, int act_stride, int inter, cudaStream_t stream) {
+                                 int top, void* act, int act_stride, int inter, cudaStream_t stream, int mode, float scale) {
     if (n_tokens == 0) return cudaSuccess;
     if (experts < 1 || experts > kMaxExperts || top < 1 || top > experts || (x != nullptr && width % 8)) return cudaErrorInvalidValue;
     if (dtype == kBF16)
         return launch(route_experts_kernel<__nv_bfloat16>, n_tokens, kRouteThreads, 0, stream, logits, (const __nv_bfloat16*)x, router, width,
-                      experts, top, (__nv_bfloat16*)act, act_stride, inter);
+                      experts, top, (__nv_bfloat16*)act, act_stride, inter, mode, scale);
     return launch(route_experts_kernel<float>, n_tokens, kRouteThreads, 0, stream, logits, (const float*)x, router, width, experts, top,
-                  (float*)act, act_stride, inter);
+                  (float*)act, act_stride, inter, mode, scale);
 }
 
 }  // namespace vtb

@@ -21,7 +21,8 @@ cudaError_t launch_logits_scale_cap(float* logits, long long n, float scale, flo
 // delta: parts [n_parts, n_tokens, hidden] float, the unadded shares of a delta, added in the order of their index.
 cudaError_t launch_rmsnorm(int out_dtype, float* x, const void* delta, const float* parts, int n_parts,
                            const float* weight, float eps, void* out, const int* rows, int n_rows, int n_tokens,
-                           int hidden, int* status, const float* post_weight, float post_eps, float post_mult, cudaStream_t stream);
+                           int hidden, int* status, const float* post_weight, float post_eps, float post_mult, cudaStream_t stream,
+                           int groups = 1, float x_scale = 1.f, int write_normed = 0);
 
 // The same with the mean taken off: out[r] = weight * (v - mean(v)) * rsqrt(mean((v - mean(v))^2) + eps).
 cudaError_t launch_layernorm(int out_dtype, float* x, const void* delta, const float* parts, int n_parts,
@@ -76,7 +77,7 @@ cudaError_t launch_attention_general(int dtype, const void* y, int stride, int q
                                      const int* token_seq, const int* block_table, int table_stride, int n_seqs, int n_pages,
                                      int n_tokens, int heads, int kv_heads, int dim, int v_dim, int page_size, int window,
                                      int chunk, float scale, int* status, int keep_first, int maps, float lam, float sub_eps,
-                                     cudaStream_t stream);
+                                     cudaStream_t stream, const float* sinks = nullptr, int v_stride = 0);
 
 // Differential attention on the tensor cores (attention_diff.cu), bfloat16: the two maps of attention_general with
 // maps 2, for the sizes that attention_diff_supports names.  tiles [n_tiles, 2] (sequence, first token), or null for a
@@ -94,7 +95,7 @@ cudaError_t launch_attention_diff(const void* y, int y_stride, int q_col, void* 
 cudaError_t launch_retention_scan(int dtype, const void* y, int stride, int q_col, int k_col, int v_col, const float* decay,
                                   float k_scale, const float* freq, int half, const int* positions, float* state, int state_rows,
                                   const int* cu_q, const int* rows, int n_seqs, float* out, int heads, int dim, int v_dim,
-                                  int most_threads, int* status, float* ends, int end_rows, cudaStream_t stream);
+                                  int most_threads, int* status, float* ends, int end_rows, cudaStream_t stream, int act = 0);
 // A long walk cut into segments (see recurrent.cu): rows[i] = -(n + 1) above starts segment i from zeros and leaves its
 // last state in ends[n].  Carry: for split sequence s with later segments first .. first + count - 1 of lengths seg_len:
 // starts[n] = the state before later segment n, and the request's row gets the last state.  Fix: tiles (later segment,
@@ -104,7 +105,7 @@ cudaError_t launch_retention_carry(float* state, int state_rows, const float* en
                                    int heads, int dim, int v_dim, int* status, cudaStream_t stream);
 cudaError_t launch_retention_fix(int dtype, const void* y, int stride, int q_col, const int* positions, const float* freq, int half,
                                  const float* starts, const int* tiles, int n_tiles, const float* decay, float* out, int heads, int dim,
-                                 int v_dim, cudaStream_t stream);
+                                 int v_dim, cudaStream_t stream, int act = 0);
 
 // Mixture of experts (experts.cu): for each row of logits [n_tokens, experts] the `top` largest choose the experts, the
 // softmax over the chosen logits weighs them; act[t, e * inter + i] *= weight of e (0 where e was not chosen), for
@@ -112,17 +113,44 @@ cudaError_t launch_retention_fix(int dtype, const void* y, int stride, int q_col
 // The logits are given, or (x not null) formed in the kernel: logits[t, e] = x[t, :] . router[e, :] in 32-bit, x of `dtype`
 // [n_tokens, width], router float [experts, width].
 cudaError_t launch_route_experts(int dtype, const float* logits, const void* x, const float* router, int width, int n_tokens, int experts,
-                                 int top, void* act, int act_stride, int inter, cudaStream_t stream);
+                                 int top, void* act, int act_stride, int inter, cudaStream_t stream, int mode = 0, float scale = 1.f);
 // The grouped form: ids / weights [n_tokens, top] of each token's picks; lists [experts, list_stride] of the picks (flat
 // index t * top + k) of every expert in rising order and counts [experts]; sorted [n_picks, width] the input rows by
 // expert and where [n_picks] each pick's row; out[t] = sum_k weights[t, k] * y[where[t * top + k]] (+ shared_y[t]).
 cudaError_t launch_route_topk(int x_dtype, const float* logits, const void* x, const float* router, int width, int n_tokens, int experts,
-                              int top, int* ids, float* weights, cudaStream_t stream);
+                              int top, int* ids, float* weights, cudaStream_t stream, int mode = 0, float scale = 1.f);
 cudaError_t launch_expert_lists(const int* ids, int n_picks, int experts, int list_stride, int* lists, int* counts, cudaStream_t stream);
 cudaError_t launch_gather_picks(int dtype, const void* x, int width, const int* lists, int list_stride, const int* counts, int experts,
                                 int top, int n_picks, void* sorted, int* where, cudaStream_t stream);
 cudaError_t launch_combine_picks(int dtype, const void* y, int width, const int* where, const float* weights, int top, int n_tokens,
                                  const void* shared_y, void* out, cudaStream_t stream);
+
+// Layers with a latent for each token (latent.cu).
+// Token shift: out[t] = x[t] + (x[t - 1] - x[t]) * mu [width]; before a sequence's first token of the step comes the row
+// state[rows[seq]] (float [state_rows, width]), which then takes the sequence's last row of the step.
+cudaError_t launch_token_shift(int out_dtype, const float* x, const float* mu, float* state, int state_rows, const int* cu_q,
+                               const int* rows, const int* token_seq, int n_seqs, void* out, int n_tokens, int width, int* status,
+                               cudaStream_t stream);
+// The two latents of a token: y[t, q_col : q_col + q_rank] normed (root mean square, q_weight) into cq [tokens, cq_stride];
+// y[t, kv_col : kv_col + kv_rank] normed (k_weight) and the rot_dim numbers behind it rotated (pairs (2i, 2i + 1), i < half,
+// angle positions[t] * freq[i], cos and sin times mult) into the token's row of pages [n_pages, 1, page_size, kv_rank + rot_dim].
+cudaError_t launch_latent_prepare(int dtype, const void* y, int stride, int q_col, int q_rank, int kv_col, int kv_rank, int rot_dim,
+                                  const float* q_weight, const float* k_weight, float eps, const float* freq, int half, float mult,
+                                  const int* positions, const int* token_seq, const int* block_table, int table_stride, int n_seqs,
+                                  int n_pages, int page_size, void* cq, int cq_stride, void* pages, int store, int n_tokens, int* status,
+                                  cudaStream_t stream);
+// out[t, out_col + h out_head + j] = sum_i x[t, x_col + h x_head + i] m[h, i, j] (m [heads, inner, outer] of m_dtype), 32-bit sums.
+// mode 1: the `tail` numbers behind a head's inputs are rotated like the shared key part and copied behind its outputs;
+// mode 2: the output is multiplied by sigmoid(gate[t, gate_col + h outer + j]) (gate may be null).
+cudaError_t launch_head_matmul(int dtype, int m_dtype, const void* x, int x_stride, int x_col, int x_head, const void* m, int heads,
+                               int inner, int outer, void* out, int out_stride, int out_col, int out_head, int n_tokens, int mode,
+                               int tail, const float* freq, int half, float mult, const int* positions, const int* token_seq,
+                               const void* gate, int gate_stride, int gate_col, cudaStream_t stream);
+// out = z > 0 ? ap z^2 + z / 2 : an (exp(z) - 1 - z) + z / 2, element by element.
+cudaError_t launch_xielu(int dtype, const void* z, void* out, long long n, float ap, float an, cudaStream_t stream);
+// out[t, i] = g sigmoid(alpha g) (u + 1), g = min(gate, lim), u = clamp(up, -lim, lim); lim = limit2 from column `split` on.
+cudaError_t launch_gate_clamp(int dtype, const void* gu, void* out, int n_tokens, int inter, int interleave, float alpha, float limit,
+                              int split, float limit2, cudaStream_t stream);
 
 // dst[t, dst_col + i] = scale * src[t, i] for src [n_tokens, n] and dst [n_tokens, dst_stride], the product in 32-bit.
 cudaError_t launch_scale_into(int dtype, const void* src, void* dst, int n_tokens, int n, int dst_stride, int dst_col, float scale,

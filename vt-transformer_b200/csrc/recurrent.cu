@@ -57,6 +57,7 @@ struct ScanArgs {
     // state of zeros and leaves its last state in ends[n] instead of a request's row
     float* ends;                  // [end rows, heads, dim, v_dim]
     int end_rows;
+    int act;                      // 1: q, k and v pass through silu (in 32-bit) while they are staged; 0: as they are
 };
 
 __device__ __forceinline__ float log_sigmoid(float z) {
@@ -121,7 +122,8 @@ scan_kernel(const ScanArgs a) {
             const int which = r < dim_p ? 0 : (r < 2 * dim_p ? 1 : 2), i = r - which * dim_p;
             if (i >= dim) return 0.f;
             const int col = which == 0 ? a.q_col : (which == 1 ? a.k_col : a.a_col);
-            const float v = to_float(yr[col + h * dim + i]);
+            float v = to_float(yr[col + h * dim + i]);
+            if (Fixed && a.act) v = v / (1.f + expf(-v));
             return (!Delta && which == (Fixed ? 1 : 0)) ? v * a.c2 : v;
         }
         r -= kVectors * dim_p;
@@ -130,7 +132,9 @@ scan_kernel(const ScanArgs a) {
             return Delta ? tanhf(v) : v;
         }
         r -= rank;
-        return col0 + r < v_dim ? to_float(yr[a.v_col + h * v_dim + col0 + r]) : 0.f;
+        if (col0 + r >= v_dim) return 0.f;
+        const float v = to_float(yr[a.v_col + h * v_dim + col0 + r]);
+        return (Fixed && a.act) ? v / (1.f + expf(-v)) : v;
     };
     auto place = [&](int tb, int r, float v) {
         if (r < kVectors * dim_p) {
@@ -201,7 +205,9 @@ scan_kernel(const ScanArgs a) {
 #pragma unroll
                 for (int k = 0; k < kScanValues; ++k) {
                     if (to_at[k] < 0) continue;
-                    float v = val[u][k] * times[k];
+                    float v = val[u][k];
+                    if (Fixed && a.act) v = v / (1.f + expf(-v));
+                    v *= times[k];
                     if (Delta && is_low[k]) v = tanhf(v);
                     smem[to_at[k] + (tb + u) * to_step[k]] = v;
                 }
@@ -404,12 +410,12 @@ cudaError_t launch_delta_scan(int dtype, const void* y, int stride, int r_col, i
 cudaError_t launch_retention_scan(int dtype, const void* y, int stride, int q_col, int k_col, int v_col, const float* decay,
                                   float k_scale, const float* freq, int half, const int* positions, float* state, int state_rows,
                                   const int* cu_q, const int* rows, int n_seqs, float* out, int heads, int dim, int v_dim,
-                                  int most_threads, int* status, float* ends, int end_rows, cudaStream_t stream) {
+                                  int most_threads, int* status, float* ends, int end_rows, cudaStream_t stream, int act) {
     if (n_seqs == 0) return cudaSuccess;
     if (2 * half > dim) return cudaErrorInvalidValue;
     // no low-rank gate (rank 0); the gate's bias slot carries the heads' decays, c2 the scale of k
     ScanArgs a = {y, stride, q_col, k_col, v_col, 0, 0, 0, nullptr, decay, nullptr, 0.f, k_scale, state, state_rows, cu_q, rows,
-                  out, heads, dim, v_dim, 1, 1, most_threads, status, freq, half, positions, ends, end_rows};
+                  out, heads, dim, v_dim, 1, 1, most_threads, status, freq, half, positions, ends, end_rows, act};
     return dtype == kBF16 ? launch_scan_t<__nv_bfloat16, false, true>(a, n_seqs, stream)
                           : launch_scan_t<float, false, true>(a, n_seqs, stream);
 }
@@ -457,7 +463,7 @@ template <typename T>
 __global__ void __launch_bounds__(128)
 retention_fix_kernel(const T* __restrict__ y, int stride, int q_col, const int* __restrict__ positions, const float* __restrict__ freq,
                      int half, const float* __restrict__ starts, const int4* __restrict__ tiles, const float* __restrict__ decay,
-                     float* __restrict__ out, int heads, int dim, int v_dim) {
+                     float* __restrict__ out, int heads, int dim, int v_dim, int act) {
     constexpr int TT = 32, RR = 32;
     __shared__ __align__(16) float qs[TT][RR];
     pdl_launch();
@@ -477,12 +483,16 @@ retention_fix_kernel(const T* __restrict__ y, int stride, int q_col, const int* 
             float v = 0.f;
             if (tk < n && i < dim) {
                 const T* qp = y + (size_t)(t_begin + tk) * stride + q_col + h * dim;
-                v = to_float(qp[i]);
+                auto value = [&](int at) {
+                    const float z = to_float(qp[at]);
+                    return act ? z / (1.f + expf(-z)) : z;       // as the scan stages it
+                };
+                v = value(i);
                 if (i < 2 * half) {
                     const int f = i < half ? i : i - half;
                     float sn, cs;
                     sincosf((float)positions[t_begin + tk] * freq[f], &sn, &cs);
-                    v = i < half ? v * cs - to_float(qp[i + half]) * sn : v * cs + to_float(qp[i - half]) * sn;
+                    v = i < half ? v * cs - value(i + half) * sn : v * cs + value(i - half) * sn;
                 }
             }
             qs[tk][e % RR] = v;
@@ -528,14 +538,14 @@ cudaError_t launch_retention_carry(float* state, int state_rows, const float* en
 
 cudaError_t launch_retention_fix(int dtype, const void* y, int stride, int q_col, const int* positions, const float* freq, int half,
                                  const float* starts, const int* tiles, int n_tiles, const float* decay, float* out, int heads, int dim,
-                                 int v_dim, cudaStream_t stream) {
+                                 int v_dim, cudaStream_t stream, int act) {
     if (n_tiles == 0) return cudaSuccess;
     const dim3 grid(n_tiles, heads, (v_dim + 127) / 128);
     if (dtype == kBF16)
         return launch(retention_fix_kernel<__nv_bfloat16>, grid, 128, 0, stream, (const __nv_bfloat16*)y, stride, q_col, positions, freq,
-                      half, starts, reinterpret_cast<const int4*>(tiles), decay, out, heads, dim, v_dim);
+                      half, starts, reinterpret_cast<const int4*>(tiles), decay, out, heads, dim, v_dim, act);
     return launch(retention_fix_kernel<float>, grid, 128, 0, stream, (const float*)y, stride, q_col, positions, freq, half, starts,
-                  reinterpret_cast<const int4*>(tiles), decay, out, heads, dim, v_dim);
+                  reinterpret_cast<const int4*>(tiles), decay, out, heads, dim, v_dim, act);
 }
 
 // ------------------------------------------------------------------------- norm of each head's output, gate

@@ -93,16 +93,24 @@ def _post(post):
     return (weight, float(eps), float(mult))
 
 
-def rmsnorm(x: torch.Tensor, weight: torch.Tensor, eps: float, out: torch.Tensor, delta=None,
-            rows: Optional[torch.Tensor] = None, status=None, post=None) -> torch.Tensor:
-    """out = weight * v * rsqrt(mean(v^2) + eps) over the rows ``rows`` (all) of v = x + delta, which is
+def rmsnorm(x: torch.Tensor, weight: torch.Tensor, eps: float, out, delta=None,
+            rows: Optional[torch.Tensor] = None, status=None, post=None, groups: int = 1, x_scale: float = 1.0,
+            to_stream: bool = False) -> torch.Tensor:
+    """out = weight * v * rsqrt(mean(v^2) + eps) over the rows ``rows`` (all) of v = x_scale * x + delta, which is
     written back to x.  ``delta``: None, a tensor of out's dtype, or a ``SplitSum``.  With ``post`` = (w [H] float32,
-    e, m) the delta is normed and scaled first, all in 32-bit: v = x + m * w * delta * rsqrt(mean(delta^2) + e)."""
+    e, m) the delta is normed and scaled first, all in 32-bit: v = x + m * w * delta * rsqrt(mean(delta^2) + e).
+    ``groups``: a row is cut into that many equal consecutive parts and each is divided by its own root mean square.
+    ``to_stream``: x takes the normed row (32-bit, unrounded) instead of the sum, for a layer whose norm comes after the
+    sum; ``out`` may then be None where nothing reads the rounded copy."""
     if isinstance(delta, SplitSum):
         delta = delta.shares
     if post is not None and delta is None:
         raise ValueError("rmsnorm: a delta to norm before it is added was announced and none came")
-    backend().rmsnorm(x, delta, weight, float(eps), out, rows, status, *_post(post))
+    if groups == 1 and x_scale == 1.0 and not to_stream:
+        backend().rmsnorm(x, delta, weight, float(eps), out, rows, status, *_post(post))
+    else:
+        weight_post = _post(post) if post is not None else (None, 0.0, 1.0)
+        backend().rmsnorm(x, delta, weight, float(eps), out, rows, status, *weight_post, int(groups), float(x_scale), bool(to_stream))
     return out
 
 
@@ -232,7 +240,7 @@ class _RetentionPlan:
 
 
 def retention_scan(y, q_col: int, k_col: int, v_col: int, decay: torch.Tensor, k_scale: float, frequencies, state: torch.Tensor,
-                   ctx, o: torch.Tensor, heads: int, dim: int, v_dim: int, status=None):
+                   ctx, o: torch.Tensor, heads: int, dim: int, v_dim: int, status=None, act: bool = False):
     """Retention over the step's tokens, sequence by sequence and head by head, in the order of the tokens:
     S <- decay[h] S + (k_scale * k_t) v_t^T, o_t = S^T q_t, after the first 2 * len(frequencies) dimensions of every
     head of q and k were rotated, pairs (i, i + len), by position * frequencies[i] (a 32-bit product, in 32-bit;
@@ -243,8 +251,9 @@ def retention_scan(y, q_col: int, k_col: int, v_col: int, decay: torch.Tensor, k
     A sequence that brings many tokens is cut into segments that run side by side: the recurrence is linear in the
     state it starts from, so the later segments start from zeros, one kernel carries the state from segment to segment,
     and one adds decay^(t - t0 + 1) S_before^T q_t to the later segments' tokens; 32-bit throughout, only the order of
-    the sums differs."""
+    the sums differs.  ``act``: q, k and v pass through silu (z / (1 + exp(-z)), 32-bit) as they are read."""
     be = backend()
+    act = 1 if act else 0
     plan = None
     if ctx.seqs and ctx.max_q_len >= 2 * RETENTION_SEGMENT_MIN and RETENTION_SEGMENTS > 1:
         key = ("retention_plan", RETENTION_SEGMENT_MIN, RETENTION_SEGMENTS)
@@ -253,17 +262,17 @@ def retention_scan(y, q_col: int, k_col: int, v_col: int, decay: torch.Tensor, k
             plan = ctx.extras[key] = _RetentionPlan(ctx, y.device)
     if plan is None or not plan.n_later:
         be.retention_scan(y, int(q_col), int(k_col), int(v_col), decay, float(k_scale), frequencies, ctx.positions, state,
-                          ctx.cu_q, ctx.rows, o, int(heads), int(dim), int(v_dim), status, _scan_threads(ctx))
+                          ctx.cu_q, ctx.rows, o, int(heads), int(dim), int(v_dim), status, _scan_threads(ctx), None, act)
         return o
     ends = torch.empty((plan.n_later, heads, dim, v_dim), dtype=torch.float32, device=y.device)
     starts = torch.empty_like(ends)
     threads = SCAN_WALK_THREADS if ctx.n_tokens >= 16 * plan.n_segments else 0
     be.retention_scan(y, int(q_col), int(k_col), int(v_col), decay, float(k_scale), frequencies, ctx.positions, state, plan.cu,
-                      plan.rows, o, int(heads), int(dim), int(v_dim), status, threads, ends)
+                      plan.rows, o, int(heads), int(dim), int(v_dim), status, threads, ends, act)
     global launches
     launches += 2
     be.retention_carry(state, ends, starts, plan.seq_row, plan.seq_first, plan.seq_count, plan.seg_len, decay, status)
-    be.retention_fix(y, int(q_col), ctx.positions, frequencies, starts, plan.tiles, decay, o)
+    be.retention_fix(y, int(q_col), ctx.positions, frequencies, starts, plan.tiles, decay, o, act)
     return o
 
 
@@ -285,17 +294,19 @@ def attention_prepare(y, q_col: int, k_col: int, v_col: int, ctx, frequencies, n
 
 def attention_general(y, q_col: int, out, out_col: int, out_scale: float, k_cache, v_cache, ctx, block_table, heads: int,
                       kv_heads: int, dim: int, v_dim: int, window, chunk, scale: float, status=None, keep_first: int = 0,
-                      maps: int = 1, lam: float = 0.0, sub_eps: float = 0.0):
+                      maps: int = 1, lam: float = 0.0, sub_eps: float = 0.0, sinks=None, values_in_keys: bool = False):
     """out[t, out_col + h * v_dim + :] = out_scale * softmax(scale * q . k_j) v_j over the keys j that token t at
     position p sees: j <= p, and j > p - window or j < keep_first (if a window is given), and j // chunk == p // chunk
     (if chunks are).  q is read at column ``q_col`` of ``y``; keys of size ``dim`` and values of size ``v_dim`` from
     their pages.  ``maps`` 2: every head has two queries [2, dim] and every head of values two heads of keys (k pages
     [pages, kv_heads * 2, page_size, dim]); with a_1 and a_2 the two attentions over the same values,
-    o = a_1 - lam * a_2 and out = out_scale * o / sqrt(mean(o^2) + sub_eps), all in 32-bit."""
+    o = a_1 - lam * a_2 and out = out_scale * o / sqrt(mean(o^2) + sub_eps), all in 32-bit.
+    ``sinks`` [heads] float32: one more term exp(sinks[h]) in the softmax's denominator, without a key or a value and not
+    scaled.  ``values_in_keys``: a value is the first ``v_dim`` numbers of its key's row (``v_cache`` is ``k_cache``)."""
     backend().attention_general(y, int(q_col), out, int(out_col), float(out_scale), k_cache, v_cache, ctx.positions,
                                 ctx.token_seq, block_table, int(heads), int(kv_heads), int(dim), int(v_dim),
                                 int(window) if window else 0, int(chunk) if chunk else 0, float(scale), status,
-                                int(keep_first), int(maps), float(lam), float(sub_eps))
+                                int(keep_first), int(maps), float(lam), float(sub_eps), sinks, bool(values_in_keys))
     return out
 
 
@@ -305,12 +316,17 @@ def attention_general(y, q_col: int, out, out_col: int, out_scale: float, k_cach
 EXPERTS_GROUPED_MIN_PICKS = int(os.environ.get("VTB200_EXPERTS_GROUPED_MIN_PICKS", "1024"))
 
 
-def route_topk(logits, top: int, ids: torch.Tensor, weights: torch.Tensor, x=None, router=None) -> None:
+_ROUTER_WEIGHTS = {"softmax": 0, "sigmoid_share": 1}
+
+
+def route_topk(logits, top: int, ids: torch.Tensor, weights: torch.Tensor, x=None, router=None, weights_by: str = "softmax",
+               scale: float = 1.0) -> None:
     """ids[t, k] and weights[t, k]: the ``top`` largest router logits of every token in falling order (the lower index
     among equals) and the softmax over them.  ``logits`` [tokens, experts] float32, or None with the tokens' input rows
     ``x`` [tokens, width] and the router's matrix ``router`` [experts, width] (float32), from which the kernel forms
-    them as 32-bit dot products."""
-    backend().route_topk(logits, int(top), ids, weights, x, router)
+    them as 32-bit dot products.  ``weights_by`` "sigmoid_share": a pick weighs as sigmoid(logit) over the picks' sum of
+    them (+ 1e-20), times ``scale``."""
+    backend().route_topk(logits, int(top), ids, weights, x, router, _ROUTER_WEIGHTS[weights_by], float(scale))
 
 
 def expert_lists(ids: torch.Tensor, lists: torch.Tensor, counts: torch.Tensor) -> None:
@@ -353,14 +369,63 @@ def attention_differential(y, q_col: int, out, out_col: int, out_scale: float, k
                                          sub_eps=sub_eps)
 
 
-def route_experts(logits, top: int, act: torch.Tensor, inter: int, x=None, router=None) -> torch.Tensor:
+def route_experts(logits, top: int, act: torch.Tensor, inter: int, x=None, router=None, weights_by: str = "softmax",
+                  scale: float = 1.0) -> torch.Tensor:
     """For every token (row): the ``top`` largest of its router logits [experts] (float32; the lower index among
     equals) choose its experts, the softmax over the chosen logits weighs them; columns [e * inter, (e + 1) * inter) of
     ``act`` (what expert e's last product multiplies) are multiplied by expert e's weight, and set to zero for an
     expert that was not chosen.  Columns beyond experts * inter (an expert that every token uses) stay.  ``logits`` may be
-    None with ``x`` and ``router`` given, as for ``route_topk``."""
-    backend().route_experts(logits, int(top), act, int(inter), x, router)
+    None with ``x`` and ``router`` given, and ``weights_by`` and ``scale``, as for ``route_topk``."""
+    backend().route_experts(logits, int(top), act, int(inter), x, router, _ROUTER_WEIGHTS[weights_by], float(scale))
     return act
+
+
+def token_shift(x: torch.Tensor, mu: torch.Tensor, state: torch.Tensor, ctx, out: torch.Tensor, status=None) -> torch.Tensor:
+    """out[t] = x[t] + (x[t - 1] - x[t]) * mu for the 32-bit rows x [T, width], mu [width] float32; the row before a
+    sequence's first token of the step is state[ctx.rows[seq]] (float32 [request rows, width], zeros at admission), which
+    then takes the sequence's last row of the step.  Rows of padding tokens become zero."""
+    backend().token_shift(x, mu, state, ctx.cu_q, ctx.rows, ctx.token_seq, out, status)
+    return out
+
+
+def latent_prepare(y, q_col: int, q_rank: int, kv_col: int, kv_rank: int, rot_dim: int, q_weight, k_weight, eps: float,
+                   frequencies, mult: float, ctx, block_table, cq, pages, store: bool = True, status=None) -> None:
+    """The two latents of every token, from the columns of ``y``: [q_col, q_col + q_rank) divided by its root mean square
+    and multiplied by ``q_weight`` goes to cq[:, :q_rank]; [kv_col, kv_col + kv_rank) the same with ``k_weight``, and the
+    ``rot_dim`` numbers behind it with their first 2 * len(frequencies) rotated (pairs (2i, 2i + 1), angle
+    position * frequencies[i] as a 32-bit product, cos and sin times ``mult``; not normed), go side by side into the
+    token's row of ``pages`` [pages, 1, page_size, kv_rank + rot_dim] if ``store``.  Norms and rotation in 32-bit."""
+    backend().latent_prepare(y, int(q_col), int(q_rank), int(kv_col), int(kv_rank), int(rot_dim), q_weight, k_weight, float(eps),
+                             frequencies, float(mult), ctx.positions, ctx.token_seq, block_table, cq, pages, bool(store), status)
+
+
+def head_matmul(x, x_col: int, x_head: int, m, out, out_col: int, out_head: int, mode: str = "plain", tail: int = 0,
+                frequencies=None, mult: float = 1.0, ctx=None, gate=None, gate_col: int = 0):
+    """out[t, out_col + h * out_head + j] = sum_i x[t, x_col + h * x_head + i] * m[h, i, j] for m [heads, inner, outer], the
+    sums in 32-bit in the order of i.  ``mode`` "rotated_tail": the ``tail`` numbers behind a head's inputs are rotated
+    like ``latent_prepare``'s shared key part and copied behind the head's outputs; "gate": the result is multiplied by
+    sigmoid(gate[t, gate_col + h * outer + j]) where ``gate`` is given."""
+    code = {"plain": 0, "rotated_tail": 1, "gate": 2}[mode]
+    backend().head_matmul(x, int(x_col), int(x_head), m, out, int(out_col), int(out_head), code, int(tail), frequencies,
+                          float(mult), None if ctx is None else ctx.positions, None if ctx is None else ctx.token_seq, gate,
+                          int(gate_col))
+    return out
+
+
+def xielu(z: torch.Tensor, out: torch.Tensor, a_pos: float, a_neg: float) -> torch.Tensor:
+    """out = a_pos z^2 + z / 2 where z > 0, a_neg (exp(z) - 1 - z) + z / 2 elsewhere; 32-bit, one rounding."""
+    backend().xielu(z, out, float(a_pos), float(a_neg))
+    return out
+
+
+def gate_clamp(gu: torch.Tensor, out: torch.Tensor, interleave: int, alpha: float, limit: float, split: int = 0,
+               limit2: Optional[float] = None) -> torch.Tensor:
+    """out = g sigmoid(alpha g) (u + 1) with g = min(gate, limit), u = clamp(up, -limit, limit); gu [T, 2 n] holds gate and
+    up side by side or, with ``interleave`` 8, alternating in runs of 8.  Columns of out from ``split`` on take ``limit2``."""
+    n = out.shape[1]
+    backend().gate_clamp(gu, out, int(interleave), float(alpha), float(limit), int(split) if limit2 is not None else n,
+                         float(limit if limit2 is None else limit2))
+    return out
 
 
 def scale_into(src: torch.Tensor, dst: torch.Tensor, dst_col: int, scale: float) -> torch.Tensor:
@@ -799,5 +864,5 @@ def _counted(fn):
 
 
 for _name in ("embedding", "logits_scale_cap", "rmsnorm", "layernorm", "polynorm", "scale_into", "head_norm_gate", "gla_scan", "delta_scan", "retention_scan", "route_experts", "attention_differential", "route_topk", "expert_lists", "gather_picks", "combine_picks",
-              "attention_prepare", "attention_general", "silu_mul", "rope_store", "linear", "paged_attention", "argmax", "sample"):  # the others count where they launch
+              "token_shift", "latent_prepare", "head_matmul", "xielu", "gate_clamp", "attention_prepare", "attention_general", "silu_mul", "rope_store", "linear", "paged_attention", "argmax", "sample"):  # the others count where they launch
     globals()[_name] = _counted(globals()[_name])

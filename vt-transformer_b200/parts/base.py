@@ -112,6 +112,13 @@ class KVCacheSpec:
 
 
 @dataclass(frozen=True)
+class LatentCacheSpec:
+    """One row of ``width`` numbers for each token, in pages (a latent from which a layer makes every head's keys and
+    values, with a key part that the heads share behind it); all tokens are kept."""
+    width: int
+
+
+@dataclass(frozen=True)
 class StateSpec:
     """A block of fixed size for each request, zero when the request is admitted."""
     shape: Tuple[int, ...]
@@ -161,6 +168,7 @@ def cache_layout(spec):
 register_cache_kind(KVCacheSpec, lambda s: PagedLayout((("k", s.kv_heads * s.k_maps, s.head_dim),
                                                         ("v", s.kv_heads, s.v_dim if s.v_dim else s.head_dim)), s.window,
                                                        s.keep_first if s.window is not None else 0))
+register_cache_kind(LatentCacheSpec, lambda s: PagedLayout((("c", 1, s.width),), None, 0))
 register_cache_kind(StateSpec, lambda s: StateLayout(tuple(s.shape), s.dtype))
 
 

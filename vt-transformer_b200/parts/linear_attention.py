@@ -169,3 +169,50 @@ class Retention(_Recurrent):
                            cache.state, ctx, o, s.heads, s.dim, s.v_dim, status=ctx.status)
         ops.head_norm_gate(o, y, cols[3], self.ones, False, s.norm_eps, "silu", out, out_col, out_scale, s.heads, s.v_dim,
                            token_seq=ctx.token_seq)
+
+
+@register_part("mixer", "lightning")
+class Lightning(_Recurrent):
+    """See ``LightningSpec``.  Projections q, k, v and gate are one product; the scan kernel passes q, k and v through silu
+    in 32-bit while it stages them and walks the tokens with the head's decay (the retention walk without a rotation or a
+    scale of k); a second kernel norms the heads' results together, multiplies by the weight and by sigmoid(gate)."""
+
+    def __init__(self, spec, prefix, rt):
+        super().__init__(spec, prefix, rt)
+        if len(spec.decay) != spec.heads:
+            raise ValueError(f"lightning: {len(spec.decay)} decays for {spec.heads} heads")
+
+    def cache_spec(self):
+        s = self.spec
+        return StateSpec((s.heads, s.dim, s.v_dim), torch.float32)
+
+    def param_specs(self):
+        s, p = self.spec, self.prefix
+        q, k, v, g, o, norm = s.names
+        hd, hv = s.heads * s.dim, s.heads * s.v_dim
+        return {p + q: ParamSpec((hd, s.hidden)), p + k: ParamSpec((hd, s.hidden)), p + v: ParamSpec((hv, s.hidden)),
+                p + g: ParamSpec((hv, s.hidden)), p + o: ParamSpec((s.hidden, hv)),
+                p + norm: ParamSpec((hv,), role="vector", init="one_plus_normal")}
+
+    def load(self, get) -> None:
+        s, p, rt = self.spec, self.prefix, self.rt
+        q, k, v, g, o, norm = s.names
+        self._in = [rt.param(get(p + n)) for n in (q, k, v, g)]
+        self.w_o = rt.param(get(p + o))
+        self.norm = rt.param(get(p + norm), "vector")
+        self.decay = torch.tensor(list(s.decay), dtype=torch.float64).to(torch.float32).to(rt.device)
+        self._small = (self.decay, self.norm)
+        self.pack()
+
+    def inner_size(self) -> int:
+        return self.spec.heads * self.spec.v_dim
+
+    def core(self, y, cols, ctx, cache, out, out_col, out_scale) -> None:
+        s, ops = self.spec, self.rt.ops
+        n = s.heads * s.v_dim
+        o = torch.empty((y.shape[0], n), dtype=torch.float32, device=y.device)
+        ops.retention_scan(y, cols[0], cols[1], cols[2], self.decay, 1.0, None, cache.state, ctx, o, s.heads, s.dim, s.v_dim,
+                           status=ctx.status, act=True)
+        # the heads are normed together: one "head" as wide as all of them, with a weight for every channel
+        ops.head_norm_gate(o, y, cols[3], self.norm, True, s.norm_eps, "sigmoid", out, out_col, out_scale, 1, n,
+                           token_seq=ctx.token_seq)

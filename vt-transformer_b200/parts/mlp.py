@@ -93,6 +93,50 @@ class PolyNormMLP(FeedForward):
         return ops.linear_to_stream(z, self.w_down, None, then=self.then)
 
 
+@register_part("feed_forward", "xielu_mlp")
+class XieluMLP(FeedForward):
+    """See ``XieluMLPSpec``: down(act(up(h) + b_up)) + b_down.  The two numbers of the activation become
+    a_pos = softplus(p) and a_neg = 1/2 + softplus(q) once, when the weights are loaded; the activation's kernel works in
+    32-bit on the product's result.  An inner size that is no multiple of 8 is zero-padded (act(0) = 0)."""
+
+    graph_safe = True
+
+    def param_specs(self):
+        s, p = self.spec, self.prefix
+        u, d, act = s.names
+        return {f"{p}{u}": ParamSpec((s.inter, s.hidden)), f"{p}{u}{s.bias_suffix}": ParamSpec((s.inter,), role="vector"),
+                f"{p}{d}": ParamSpec((s.hidden, s.inter)), f"{p}{d}{s.bias_suffix}": ParamSpec((s.hidden,), role="vector"),
+                f"{p}{act}": ParamSpec((2,), role="vector")}
+
+    def load(self, get) -> None:
+        import math
+        from .projected import pack_columns, pack_rows
+        s, p, rt = self.spec, self.prefix, self.rt
+        u, d, act = s.names
+        self.w_up, _ = pack_rows([rt.param(get(f"{p}{u}"))])
+        self.w_down, _, _ = pack_columns([rt.param(get(f"{p}{d}"))])
+        b_up = rt.param(get(f"{p}{u}{s.bias_suffix}"), "vector")
+        pad = self.w_up.shape[0] - b_up.numel()
+        self.b_up = torch.cat([b_up, torch.zeros(pad, dtype=b_up.dtype, device=b_up.device)]).contiguous() if pad else b_up
+        self.b_down = rt.param(get(f"{p}{d}{s.bias_suffix}"), "vector")
+        two = [float(v) for v in get(f"{p}{act}").double().flatten().tolist()]
+        softplus = lambda v: max(v, 0.0) + math.log1p(math.exp(-abs(v)))
+        self.a_pos, self.a_neg = softplus(two[0]), 0.5 + softplus(two[1])
+
+    def weight_bytes(self) -> int:
+        return sum(m.numel() * m.element_size() for m in (self.w_up, self.w_down, self.b_up, self.b_down))
+
+    def first_product(self):
+        return self.rt.ops.product_hint(self.w_up, "linear")
+
+    def forward(self, h, ctx):
+        ops = self.rt.ops
+        z = torch.empty((h.shape[0], self.w_up.shape[0]), dtype=h.dtype, device=h.device)
+        ops.linear(h, self.w_up, self.b_up, z, then=ops.product_hint(self.w_down, "stream"))
+        ops.xielu(z, z, self.a_pos, self.a_neg)
+        return ops.linear_to_stream(z, self.w_down, self.b_down, then=self.then)
+
+
 @register_part("feed_forward", "experts")
 class Experts(FeedForward):
     """See ``ExpertsSpec``.  The router's logits are 32-bit dot products formed inside the routing kernel (its matrix is
@@ -111,6 +155,23 @@ class Experts(FeedForward):
     twice (packed along the inner dimension for the one product, one by one for the grouped products)."""
 
     graph_safe = True
+
+    def __init__(self, spec, prefix, rt):
+        super().__init__(spec, prefix, rt)
+        if spec.activation not in ("silu", "clamped"):
+            raise ValueError(f"experts: activation '{spec.activation}' is not built; known: silu, clamped")
+        if spec.router_weights not in ("softmax", "sigmoid_share"):
+            raise ValueError(f"experts: router weights '{spec.router_weights}' are not built; known: softmax, sigmoid_share")
+
+    def gate_up(self, x, w_gate_up, act, limit: float, then=None, split: int = 0, limit2=None):
+        """act = what the last product multiplies, from x and the interleaved gate and up matrices: silu(gate) * up in the
+        product's epilogue, or, for the clamped form, the product and then the activation's kernel."""
+        s, ops = self.spec, self.rt.ops
+        if s.activation == "silu":
+            return ops.linear_silu_mul(x, w_gate_up, act, then=then)
+        gu = torch.empty((x.shape[0], w_gate_up.shape[0]), dtype=x.dtype, device=x.device)
+        ops.linear(x, w_gate_up, None, gu)
+        return ops.gate_clamp(gu, act, 8, s.gate_alpha, limit, split=split, limit2=limit2)
 
     def param_specs(self):
         s, p = self.spec, self.prefix
@@ -168,8 +229,10 @@ class Experts(FeedForward):
         if ctx.max_q_len > 1 and T * s.top >= ops.EXPERTS_GROUPED_MIN_PICKS:
             return self.grouped(h)
         act = torch.empty((T, self.w_down.shape[1]), dtype=h.dtype, device=h.device)
-        ops.linear_silu_mul(h, self.w_gate_up, act, then=ops.product_hint(self.w_down, "stream"))
-        ops.route_experts(None, s.top, act, self.inter, x=h, router=self.router)     # the router's logits are formed there, in 32-bit
+        self.gate_up(h, self.w_gate_up, act, s.limit, then=ops.product_hint(self.w_down, "stream"),
+                     split=s.experts * self.inter, limit2=s.shared_limit if s.shared_inter else None)
+        # the router's logits are formed there, in 32-bit
+        ops.route_experts(None, s.top, act, self.inter, x=h, router=self.router, weights_by=s.router_weights, scale=s.router_scale)
         return ops.linear_to_stream(act, self.w_down, None, then=self.then)
 
     def grouped(self, h):
@@ -178,7 +241,7 @@ class Experts(FeedForward):
         T, picks = h.shape[0], h.shape[0] * s.top
         ids = torch.empty((T, s.top), dtype=torch.int32, device=dev)
         weights = torch.empty((T, s.top), dtype=torch.float32, device=dev)
-        ops.route_topk(None, s.top, ids, weights, x=h, router=self.router)
+        ops.route_topk(None, s.top, ids, weights, x=h, router=self.router, weights_by=s.router_weights, scale=s.router_scale)
         lists = torch.empty((s.experts, T), dtype=torch.int32, device=dev)
         counts = torch.empty((s.experts,), dtype=torch.int32, device=dev)
         ops.expert_lists(ids, lists, counts)
@@ -188,7 +251,7 @@ class Experts(FeedForward):
         shared_y = None
         if s.shared_inter:          # the shared expert's products are enqueued before the host waits for the counts
             act = torch.empty((T, self.down_of[-1].shape[1]), dtype=h.dtype, device=dev)
-            ops.linear_silu_mul(h, self.gate_up_of[-1], act)
+            self.gate_up(h, self.gate_up_of[-1], act, s.shared_limit)
             shared_y = torch.empty((T, s.hidden), dtype=h.dtype, device=dev)
             ops.linear(act, self.down_of[-1], None, shared_y)
         act = torch.empty((picks, self.inter), dtype=h.dtype, device=dev)
@@ -196,7 +259,7 @@ class Experts(FeedForward):
         at = 0
         for e, n in enumerate(counts.tolist()):
             if n:
-                ops.linear_silu_mul(rows[at:at + n], self.gate_up_of[e], act[at:at + n])
+                self.gate_up(rows[at:at + n], self.gate_up_of[e], act[at:at + n], s.limit)
                 ops.linear(act[at:at + n], self.down_of[e], None, y[at:at + n])
             at += n
         out = torch.empty((T, s.hidden), dtype=h.dtype, device=dev)

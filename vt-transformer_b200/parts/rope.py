@@ -76,3 +76,39 @@ class ComputedRotary(PositionEncoding):
     def load(self, get) -> None:
         self.frequencies = (rotation_frequencies(self.spec.dim, self.spec.base, self.spec.scaling).to(self.rt.device)
                             if self.spec.dim else None)
+
+
+def ramped_frequencies(dim: int, base: float, ramp=None):
+    """([dim / 2] float32, m): f_i = base^(-2i/dim) in double, rounded once.  ``ramp`` = (factor, original, fast, slow): with
+    n(t) = dim ln(original / (2 pi t)) / (2 ln base), lo = max(floor(n(fast)), 0), hi = min(ceil(n(slow)), dim - 1) and
+    r_i = clamp((i - lo) / max(hi - lo, 0.001), 0, 1), pair i turns with f_i / factor * r_i + f_i (1 - r_i), and
+    m = 0.1 ln(factor) + 1 multiplies cos and sin (1 without a ramp)."""
+    f = [math.pow(float(base), -2.0 * i / dim) for i in range(dim // 2)]
+    mult = 1.0
+    if ramp is not None:
+        factor, original, fast, slow = (float(v) for v in ramp)
+
+        def pair_of(turns: float) -> float:
+            return dim * math.log(original / (2.0 * math.pi * turns)) / (2.0 * math.log(float(base)))
+
+        lo = max(math.floor(pair_of(fast)), 0)
+        hi = min(math.ceil(pair_of(slow)), dim - 1)
+        for i in range(len(f)):
+            r = min(1.0, max(0.0, (i - lo) / max(hi - lo, 0.001)))
+            f[i] = f[i] / factor * r + f[i] * (1.0 - r)
+        mult = 0.1 * math.log(factor) + 1.0
+    return torch.tensor(f, dtype=torch.float64).to(torch.float32), mult
+
+
+@register_part("position", "rotary_interleaved")
+class InterleavedRotary(PositionEncoding):
+    """The rotation of the first ``dim`` dimensions of a vector in pairs (2i, 2i + 1), the angle position * f_i formed as a
+    32-bit product where it is used, cos and sin multiplied by ``mult``.  Holds the [dim/2] frequencies on the device."""
+
+    table = None
+
+    def load(self, get) -> None:
+        self.frequencies, self.mult = None, 1.0
+        if self.spec.dim:
+            f, self.mult = ramped_frequencies(self.spec.dim, self.spec.base, self.spec.ramp)
+            self.frequencies = f.to(self.rt.device)

@@ -21,12 +21,15 @@ from typing import Optional, Tuple
 class NormSpec:
     """``rmsnorm``: w * x / sqrt(mean(x^2) + eps).  ``layernorm``: w * (x - mean) / sqrt(var + eps), var the mean of
     the squared deviations, no bias.  ``weight_suffix`` is appended to the part's prefix for the weight's name.
-    ``one_plus``: the stored weight lies around zero and multiplies as 1 + w."""
+    ``one_plus``: the stored weight lies around zero and multiplies as 1 + w.
+    ``groups`` (``rmsnorm``): the vector is cut into that many equal consecutive parts and each is divided by its own
+    root mean square; the weight [size] multiplies the whole."""
     size: int
     eps: float
     kind: str = "rmsnorm"
     weight_suffix: str = ".weight"
     one_plus: bool = False
+    groups: int = 1
 
 
 @dataclass(frozen=True)
@@ -37,12 +40,17 @@ class PositionSpec:
     ``none``: nothing.
     ``scaling`` (``rotary_computed``): (factor, low, high, original).  A frequency f with wavelength l = 2 pi / f is kept
     where l < original / high, divided by factor where l > original / low, and between the two it is
-    (1 - s) f / factor + s f with s = (original / l - low) / (high - low)."""
+    (1 - s) f / factor + s f with s = (original / l - low) / (high - low).
+    ``rotary_interleaved``: pairs (2i, 2i + 1) of the first ``dim`` dimensions, angle formed where it is used as for
+    ``rotary_computed``.  ``ramp`` = (factor, original, fast, slow): with n(t) = dim ln(original / (2 pi t)) / (2 ln base),
+    lo = max(floor(n(fast)), 0), hi = min(ceil(n(slow)), dim - 1) and r_i = clamp((i - lo) / max(hi - lo, 0.001), 0, 1),
+    pair i turns with f_i / factor * r_i + f_i (1 - r_i), and cos and sin are multiplied by 0.1 ln(factor) + 1."""
     dim: int = 0
     base: float = 0.0
     max_positions: int = 0
     kind: str = "rotary"
     scaling: Optional[Tuple[float, float, float, float]] = None
+    ramp: Optional[Tuple[float, float, float, float]] = None
 
 
 @dataclass(frozen=True)
@@ -115,6 +123,48 @@ class RetentionSpec(MixerSpec):
     position: PositionSpec = field(default_factory=lambda: PositionSpec(kind="none"))
     names: Tuple[str, ...] = ("q", "k", "v", "g", "o")
     kind: str = "retention"
+
+
+@dataclass(frozen=True)
+class LatentAttentionSpec(MixerSpec):
+    """Softmax attention whose keys and values are made from one narrow latent a token, which is all that is kept.
+    c_q = N(D_q h) (root mean square ``norm_eps``, weight), q = U_q c_q laid out head by head as [``head_dim`` plain |
+    ``rot_dim`` rotated].  D_kv h has ``kv_rank`` + ``rot_dim`` rows: the first, normed the same way, are the latent c; the
+    others, rotated and not normed, are a key part that all heads share.  Head i's key is [U_k,i c | shared part], its value
+    U_v,i c (``v_dim``); score = q . k * ``scale``; causal softmax, with ``sink`` one more term exp(s_i) (a number a head) in
+    the denominator; with ``gate`` the heads' results are multiplied by sigmoid(G h); then the output projection.
+    ``names``: D_q, its norm, U_q, D_kv, its norm, U_k, U_v, output, sink, gate."""
+    hidden: int = 0
+    heads: int = 0
+    head_dim: int = 0
+    rot_dim: int = 0
+    v_dim: int = 0
+    q_rank: int = 0
+    kv_rank: int = 0
+    scale: float = 1.0
+    sink: bool = False
+    gate: bool = False
+    norm_eps: float = 1e-6
+    position: PositionSpec = field(default_factory=lambda: PositionSpec(kind="none"))
+    names: Tuple[str, ...] = ("dq", "dq.norm", "uq", "dkv", "dkv.norm", "uk", "uv", "o", "sink", "g")
+    kind: str = "latent_attention"
+
+
+@dataclass(frozen=True)
+class LightningSpec(MixerSpec):
+    """Linear attention with one fixed decay a head over activated projections: q = silu(Q h), k = silu(K h),
+    v = silu(V h); for each head S [dim, v_dim] (32-bit, zero at the start of a request): S <- decay[h] S + k_t v_t^T,
+    o_t = S^T q_t, no other scale.  The heads' results together are divided by their root mean square (``norm_eps``),
+    multiplied by a weight [heads * v_dim] and by sigmoid(G h); then the output projection.  ``names``: q, k, v, gate,
+    output, the norm's weight."""
+    hidden: int = 0
+    heads: int = 0
+    dim: int = 0
+    v_dim: int = 0
+    decay: Tuple[float, ...] = ()
+    norm_eps: float = 1e-6
+    names: Tuple[str, ...] = ("q", "k", "v", "g", "o", "norm")
+    kind: str = "lightning"
 
 
 @dataclass(frozen=True)
@@ -191,16 +241,37 @@ class PolyNormMLPSpec(FeedForwardSpec):
 
 
 @dataclass(frozen=True)
+class XieluMLPSpec(FeedForwardSpec):
+    """down(act(up(x) + b_up)) + b_down with act(z) = softplus(p) z^2 + z / 2 for z > 0 and
+    (1/2 + softplus(q)) (exp(z) - 1 - z) + z / 2 for z <= 0; (p, q) a tensor of two numbers.  ``names``: up, down, the
+    two numbers; a bias is the matrix's name + ``bias_suffix``."""
+    hidden: int = 0
+    inter: int = 0
+    names: Tuple[str, str, str] = ("up", "down", "act")
+    bias_suffix: str = ".b"
+    kind: str = "xielu_mlp"
+
+
+@dataclass(frozen=True)
 class ExpertsSpec(FeedForwardSpec):
     """A mixture of ``experts`` gated feed-forwards (down(silu(gate(x)) * up(x)), inner size ``inter``, no biases) of
     which a token uses the ``top`` with the largest router logits z = R x (32-bit), weighted by the softmax over the
     chosen logits; with ``shared_inter`` an expert of that inner size runs for every token and is added.  Tensors:
-    ``router``, ``e<i>.gate|up|down``, ``shared.gate|up|down`` below the part's prefix."""
+    ``router``, ``e<i>.gate|up|down``, ``shared.gate|up|down`` below the part's prefix.
+    ``activation`` "clamped": an expert's inner vector is g sigmoid(``gate_alpha`` g) (u + 1) with g = min(gate(x), ``limit``)
+    and u = clamp(up(x), -``limit``, ``limit``) (the shared expert with ``shared_limit``).  ``router_weights`` "sigmoid_share":
+    the chosen experts weigh as sigmoid(z) over the chosen experts' sum of sigmoid(z) (+ 1e-20), times ``router_scale``."""
     hidden: int = 0
     experts: int = 0
     top: int = 1
     inter: int = 0
     shared_inter: Optional[int] = None
+    activation: str = "silu"
+    limit: float = 0.0
+    shared_limit: float = 0.0
+    gate_alpha: float = 1.702
+    router_weights: str = "softmax"
+    router_scale: float = 1.0
     names: Tuple[str, str, str] = ("gate", "up", "down")
     router_name: str = "router"
     expert_prefix: str = "e"
@@ -213,6 +284,10 @@ class BlockSpec:
     """One layer.  ``prenorm``: x += mixer(norm1(x)); x += ffn(norm2(x)).  With ``ffn`` None the layer has the
     first sublayer only (and no second norm).  ``sandwich``: x += m * post1(mixer(norm1(x))); x += m * post2(ffn(norm2(x)))
     with m = ``residual_mult`` and ``post1``, ``post2`` norms of the sublayers' results.
+    ``postnorm``: x <- norm1(a x + mixer(shift(x))); x <- norm2(a x + ffn(x)) with a = ``stream_scale``: the norms come
+    after the sums and their result is the stream.  With ``shift_name`` the mixer reads h_t + (h_(t-1) - h_t) * mu
+    (mu [hidden] the tensor of that name below the layer's prefix, h_(t-1) the previous token's x, zeros before a request's
+    first token), and the layer keeps a request's last x beside what its mixer keeps.
 
     ``prefix`` is the tensor-name prefix of the layer; ``mixer_prefix`` and the others
     are appended to it for the parts below it."""
@@ -231,6 +306,8 @@ class BlockSpec:
     post1_name: str = "norm1b"
     post2_name: str = "norm2b"
     residual_mult: float = 1.0
+    stream_scale: float = 1.0
+    shift_name: Optional[str] = None
 
 
 @dataclass(frozen=True)

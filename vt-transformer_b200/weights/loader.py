@@ -177,6 +177,8 @@ _INITIALISERS = {
     "one_plus_normal": lambda shape, g, sigma, device: torch.randn(shape, generator=g, dtype=torch.float32,
                                                                    device=device) * sigma + 1.0,
     "zeros": lambda shape, g, sigma, device: torch.zeros(shape, dtype=torch.float32, device=device),
+    # numbers between 0 and 1 (how much of the token before a token shift mixes in)
+    "unit_uniform": lambda shape, g, sigma, device: torch.rand(shape, generator=g, dtype=torch.float32, device=device),
     # the four numbers of a PolyNorm activation: three weights of the order of a half that differ, and a small offset
     "polynorm_coefficients": lambda shape, g, sigma, device: torch.tensor([0.8, 0.6, 0.3, 0.1], dtype=torch.float32, device=device)
     + torch.randn(shape, generator=g, dtype=torch.float32, device=device) * sigma,
