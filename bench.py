@@ -396,6 +396,32 @@ def _vegilix_config(width, ff, ret, att, window, pairs=2):
     return {"architecture": "Vegilix", "vocab": 32768, "width": width, "layers": layers, "norm": {"eps": 1e-6}, "residual_mult": 0.7}
 
 
+def _geponex_config(width, ff, lig, att, pairs=2):
+    """``pairs`` times (a latent-attention layer, a lightning layer): the attention alternates between the plain variant
+    (ramped rotation frequencies; 8 clamped experts of which a token uses 2 beside a shared expert, the three experts a
+    token runs having ``ff`` inner values together) and the variant with a sink and an output gate (a dense xIELU
+    feed-forward of ``ff``); the lightning layers take the experts.  ``att``: (heads, kv heads, head size) of the Qwen2 model
+    of equal size: as many heads with that plain part, a rotated part half as wide, a keys' latent of 4 heads' width and
+    a queries' latent of 12."""
+    heads, dim = att[0], att[2]
+    inner = ff // 3 // 64 * 64
+    moe = {"kind": "moe", "router": {"experts": 8, "top": 2, "scale": 1.5}, "expert": {"ff": inner, "limit": 7.0},
+           "shared": {"ff": inner, "limit": 7.0}}
+    layers = []
+    for i in range(pairs):
+        second = i % 2 == 1
+        rot = {"dims": dim // 2, "base": 1e6}
+        if not second:
+            rot["scaling"] = {"factor": 8.0, "original": 8192, "fast": 32.0, "slow": 1.0}
+        layers.append({"type": "latent_attention_2" if second else "latent_attention", "mixer": {
+            "heads": heads, "dim": dim, "rot_dim": dim // 2, "vdim": dim, "q_rank": 12 * dim, "kv_rank": 4 * dim,
+            "scale": (1.5 * dim) ** -0.5, "rot": rot}, "mlp": {"kind": "dense", "ff": ff} if second else moe})
+        layers.append({"type": "lightning", "mixer": {"heads": lig[0], "dim": lig[1], "vdim": lig[2],
+                                                      "decay": [1.0 - 2.0 ** (-5 - 0.5 * h) for h in range(lig[0])]}, "mlp": moe})
+    return {"architecture": "Geponex", "vocab": 32768, "width": width, "layers": layers, "norm": {"eps": 1e-6, "groups": 2},
+            "postln_alpha": 2.0}
+
+
 DESIGN_SIZES = {
     # name: width, feed-forward, (gla heads, dim, vdim), (attention heads, kv heads, head size), (delta heads, dim), chunk
     "w1024": (1024, 4096, (8, 64, 128), (16, 2, 64), (8, 64), 1024),
@@ -406,6 +432,7 @@ DESIGNS = {
     "sisetar": lambda width, ff, gla, att, delta, chunk: _sisetar_config(width, ff, gla, att, delta, chunk),
     # (the recurrent layer has the gated linear attention's sizes; the window is the other design's chunk)
     "vegilix": lambda width, ff, gla, att, delta, chunk: _vegilix_config(width, ff, gla, att, chunk),
+    "geponex": lambda width, ff, gla, att, delta, chunk: _geponex_config(width, ff, gla, att),
 }
 
 
@@ -442,8 +469,9 @@ def design_points(design: str, sizes, steps: int, warmup: int) -> int:
     def per_kernel(runner, entries):
         """Device time of each of the package's kernels in one eager step, by the name of the op."""
         names = [n for n in ("embedding", "rmsnorm", "layernorm", "polynorm", "head_norm_gate", "gla_scan", "delta_scan",
-                             "retention_scan", "route_experts", "attention_differential", "attention_prepare", "attention_general", "rope_store", "paged_attention", "rope_attention", "linear",
-                             "linear_silu_mul", "linear_to_stream", "logits_scale_cap")]
+                             "retention_scan", "route_experts", "route_topk", "token_shift", "latent_prepare", "head_matmul", "attention_latent", "xielu",
+                             "gate_clamp", "attention_differential", "attention_prepare", "attention_general", "rope_store", "paged_attention", "rope_attention", "linear",
+                             "linear_silu_mul", "linear_to_stream", "logits_scale_cap") if hasattr(ops, n)]
         saved, events = {n: getattr(ops, n) for n in names}, []
 
         def wrap(name, fn):

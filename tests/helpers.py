@@ -118,6 +118,9 @@ def plain_module(folder: str):
     if c.get("architecture") == "Sisetar":
         from plain import sisetar_plain
         return sisetar_plain
+    if c.get("architecture") == "Geponex":
+        from plain import geponex_plain
+        return geponex_plain
     if c.get("architecture") == "Vegilix":
         from plain import vegilix_plain
         return vegilix_plain

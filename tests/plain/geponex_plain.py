@@ -6,11 +6,31 @@ Notation: x is a token's vector in the stream, h what a sublayer reads, W_a the 
 stored [out, in] and applied as W h."""
 from __future__ import annotations
 
+import json
 import math
+import os
 
 import torch
 
 F = torch.float64
+
+
+def read_config(folder: str) -> dict:
+    with open(os.path.join(folder, "config.json")) as f:
+        return json.load(f)
+
+
+def read_weights(folder: str, dtype=F):
+    from safetensors import safe_open
+    out = {}
+    with safe_open(os.path.join(folder, "model.safetensors"), framework="pt") as f:
+        for name in f.keys():
+            out[name] = f.get_tensor(name).to(dtype)
+    return out
+
+
+def sample_greedy(logits):
+    return int(torch.argmax(logits))
 
 
 def rms_norm(v, w, eps):
@@ -155,15 +175,21 @@ def expert(h, gate, up, down, limit):
     return (g * torch.sigmoid(1.702 * g) * (u + 1.0)) @ down.T
 
 
-def route(h, router, top, scale):
-    """(ids [T, top], weights [T, top]): the experts with the largest sigmoid scores, the scores over their sum, scaled."""
-    s = torch.sigmoid(h @ router.T)
+def route(h, router, top, scale, margins=None):
+    """(ids [T, top], weights [T, top]): the experts with the largest sigmoid scores, the scores over their sum, scaled.
+    ``margins`` gets, for every token, how far the last chosen logit lies above the first that is not, as a part of the
+    largest logit's size."""
+    z = h @ router.T
+    s = torch.sigmoid(z)
+    if margins is not None and top < z.shape[1]:
+        ranked = torch.sort(z, dim=1, descending=True).values
+        margins.append((ranked[:, top - 1] - ranked[:, top]) / z.abs().max(dim=1).values.clamp_min(1e-9))
     chosen = torch.topk(s, top, dim=-1)
     return chosen.indices, chosen.values / (chosen.values.sum(dim=-1, keepdim=True) + 1e-20) * scale
 
 
-def moe_ff(h, w, f):
-    ids, weights = route(h, w["router"], f["router"]["top"], f["router"]["scale"])
+def moe_ff(h, w, f, margins=None):
+    ids, weights = route(h, w["router"], f["router"]["top"], f["router"]["scale"], margins)
     out = torch.zeros(h.shape[0], w["e0.down"].shape[0], dtype=F)
     for t in range(h.shape[0]):
         for e, wt in zip(ids[t].tolist(), weights[t]):
@@ -195,9 +221,9 @@ class Sequence:
             self.layers.append({"before": torch.zeros(config["width"], dtype=F), "mix": mix})
 
 
-def forward(config, weights, tokens, seq=None, trace=None):
+def forward(config, weights, tokens, seq=None, trace=None, margins=None):
     """Runs ``tokens`` after what ``seq`` has seen; returns logits [T, vocab].  ``trace``: a list that takes the stream
-    after every layer."""
+    after every layer.  ``margins``: a list that takes every router's margins (see ``route``)."""
     seq = seq if seq is not None else Sequence(config)
     eps, groups, alpha = config["norm"]["eps"], config["norm"]["groups"], config["postln_alpha"]
     positions = torch.arange(seq.length, seq.length + len(tokens))
@@ -215,7 +241,7 @@ def forward(config, weights, tokens, seq=None, trace=None):
         f = layer.get("mlp")
         if f is not None:
             w = sub(weights, p + "mlp.")
-            y = dense_ff(x, w) if f["kind"] == "dense" else moe_ff(x, w, f)
+            y = dense_ff(x, w) if f["kind"] == "dense" else moe_ff(x, w, f, margins)
             x = grouped_rms_norm(alpha * x + y, weights[p + "norm2"].to(F), eps, groups)
         if trace is not None:
             trace.append(x.clone())

@@ -134,8 +134,9 @@ class GeponexConfig(ModelConfig):
                 if not 0 <= j < len(self.layers) or j == i:
                     raise ConfigError(f"{at}: 'weights_of' {j} names no other layer")
                 o = self.layers[self.owner(i)]
-                if (o.type, o.mixer, o.mlp) != (layer.type, layer.mixer, layer.mlp):
-                    raise ConfigError(f"{at}: a layer that uses layer {j}'s weights must have its type, mixer and mlp")
+                if o.type != layer.type:
+                    raise ConfigError(f"{at}: 'weights_of' {j} names a layer of another type ('{o.type}'); the sizes and "
+                                      f"constants are taken from the layer that owns the weights")
             m = layer.mixer
             if layer.type == "lightning":
                 if len(m.decay) != m.heads:
