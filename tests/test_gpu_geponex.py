@@ -133,6 +133,47 @@ def test_routing_kernel_with_sigmoid_scores(experts, top):
         assert float((wts.double().cpu().sum(1) - 1.3).abs().max()) <= 1e-5
 
 
+@pytest.mark.parametrize("sink", [False, True])
+@pytest.mark.parametrize("heads,key,v_dim,page", [(4, 96, 64, 16), (8, 160, 128, 64), (3, 48, 16, 16), (16, 320, 256, 64), (6, 576, 512, 32),
+                                                  (70, 64, 32, 16), (5, 112, 80, 16)])
+def test_latent_attention_kernel_on_the_tensor_cores(heads, key, v_dim, page, sink):
+    """Rows that all heads share, their first numbers the values: a sequence that goes on from 37 cached tokens beside one
+    that starts, over shuffled pages; then a step of single tokens.  Against the plain softmax attention."""
+    from vt_transformer_b200 import ops
+    assert ops.backend().attention_latent_supports(key, v_dim)
+    g = torch.Generator().manual_seed(heads + key)
+    scale = 1.7 / math.sqrt(key)
+    sinks = torch.linspace(-1.0, 2.0, heads) if sink else None
+    lengths = [37 + 70 + 1, 5 + 1]
+    rows = [torch.randn((n, key), generator=g).to(torch.bfloat16) for n in lengths]
+    n_pages = sum(-(-n // page) for n in lengths) + 3
+    order = torch.randperm(n_pages, generator=g).tolist()
+    pages = torch.zeros((n_pages, 1, page, key), dtype=torch.bfloat16)
+    table = torch.full((2, max(-(-n // page) for n in lengths)), -1, dtype=torch.int32)
+    for s, r in enumerate(rows):
+        for j in range(-(-len(r) // page)):
+            table[s, j] = order.pop()
+            part = r[j * page:(j + 1) * page]
+            pages[table[s, j], 0, :len(part)] = part
+    pd, td = pages.to(DEV), table.to(DEV)
+    for q_lens, starts in (([70, 5], [37, 0]), ([1, 1], [107, 5])):
+        T = sum(q_lens)
+        q = torch.randn((T, heads, key), generator=g).to(torch.bfloat16)
+        ctx = helpers.step_context(q_lens, starts, DEV)
+        out = torch.full((T, heads * v_dim), 7.0, dtype=torch.bfloat16, device=DEV)
+        before = ops.launches
+        ops.attention_latent(q.view(T, -1).to(DEV), 0, out, 0, pd, ctx, td, heads, key, v_dim, scale, sinks=None if sinks is None else sinks.to(DEV))
+        assert ops.launches == before + 1
+        at = 0
+        for s, (n, start) in enumerate(zip(q_lens, starts)):
+            k = rows[s][:start + n].double()
+            ref = plain.softmax_attention(q[at:at + n].double(), k[:, None, :].expand(-1, heads, -1), k[:, None, :v_dim].expand(-1, heads, -1),
+                                          torch.arange(start, start + n), scale, None if sinks is None else sinks.double())
+            got = out[at:at + n].double().cpu().view(n, heads, v_dim)
+            assert float((got - ref).abs().max()) <= 2.5e-2, (q_lens, s)
+            at += n
+
+
 # ----------------------------------------------------------------------------- each mechanism alone, in a model of one layer
 
 
@@ -252,19 +293,27 @@ def test_a_key_hundreds_of_tokens_back_and_at_page_borders(geponex_folders, tmp_
     and with the asking tokens decoded one by one."""
     folder = cases.rewritten(geponex_folders(name), str(tmp_path / "far"), lambda t: cases.sharpen_attention(t, 4.0))
     base = cases.prompts_for(name, lengths=[392])[0]
-    ask = 389
+    plain_base = _logits(folder, base)
+    # queries four times as long make the scores' rounding in bfloat16 four times as large: twice the bound of a model of
+    # one layer there (the marked key still moves the logits by more than three times as much)
+    bound = cases.tol(dtype, plain_base, alone=True) * (2.0 if dtype == "bfloat16" else 1.0)
     runner = cases.runner_for(folder, DEV, dtype, num_pages=26, max_requests=1)
     for where in (3, 15, 16, 383):
-        marked = max(range(0, 128, 3), key=lambda tok: _sensitivity(folder, base, ask, where, tok))
+        best = (0.0, 0, 0)
+        for tok in range(0, 128, 2):                    # the token and the asking position (decoded alone below) that show it best
+            ids = list(base)
+            ids[where] = tok
+            d = (_logits(folder, ids)[384:] - plain_base[384:]).abs().max(dim=1).values
+            best = max(best, (float(d.max()), tok, 384 + int(d.argmax())))
+        assert best[0] > 3 * bound, (where, best)
         ids = list(base)
-        ids[where] = marked
+        ids[where] = best[1]
         ref = _logits(folder, ids)
-        assert float((ref[ask] - _logits(folder, base)[ask]).abs().max()) > 3 * cases.tol(dtype, ref, alone=True), where
         for cuts in ([len(ids)], [150, 37, 190] + [1] * 15, [380] + [1] * 12):
             row = runner.admit()
             got = cases.step_all(runner, row, ids, cuts)
             runner.release(row)
-            assert float((got - ref).abs().max()) <= cases.tol(dtype, ref, alone=True), (where, cuts)
+            assert float((got - ref).abs().max()) <= bound, (where, cuts)
 
 
 @pytest.mark.parametrize("dtype", DTYPES)

@@ -342,6 +342,46 @@ void attention_diff(const Tensor& y, int64_t q_col, Tensor& out, int64_t out_col
                                             (float)sub_eps, status_ptr(status), stream_of(y)), "attention_diff");
 }
 
+void attention_latent(const Tensor& q, int64_t q_col, Tensor& out, int64_t out_col, const Tensor& pages, const Tensor& cu_q,
+                      const Tensor& q_start, const Tensor& block_table, c10::optional<Tensor> tiles, int64_t heads, int64_t key,
+                      int64_t v_dim, double scale, c10::optional<Tensor> sinks) {
+    check_cuda(q, "q"); check_cuda(out, "out"); check_cuda(pages, "pages");
+    check_i32(cu_q, "cu_q"); check_i32(q_start, "q_start"); check_i32(block_table, "block_table");
+    TORCH_CHECK(q.scalar_type() == torch::kBFloat16 && out.scalar_type() == torch::kBFloat16 && pages.scalar_type() == torch::kBFloat16,
+                "attention_latent: bfloat16 only");
+    TORCH_CHECK(q.dim() == 2 && out.dim() == 2 && out.size(0) == q.size(0) && q.is_contiguous() && out.is_contiguous(),
+                "attention_latent: q and out [tokens, .]");
+    TORCH_CHECK(block_table.dim() == 2 && cu_q.numel() == q_start.numel() + 1 && block_table.size(0) >= q_start.numel(),
+                "attention_latent: cu_q [sequences + 1], q_start [sequences], block_table [sequences, stride]");
+    TORCH_CHECK(vtb::attention_latent_supports(key, v_dim), "attention_latent: sizes that the kernel does not take");
+    TORCH_CHECK(pages.dim() == 4 && pages.size(1) == 1 && pages.size(3) == key && pages.is_contiguous(),
+                "attention_latent: pages [pages, 1, page_size, key]");
+    TORCH_CHECK(q_col % 8 == 0 && out_col % 2 == 0 && q.size(1) % 8 == 0 && out.size(1) % 2 == 0,
+                "attention_latent: queries must start on 16-byte boundaries");
+    check_cols(q, q_col, heads * key, "attention_latent (q)"); check_cols(out, out_col, heads * v_dim, "attention_latent (out)");
+    const float* sp = nullptr;
+    if (sinks.has_value()) {
+        check_f32(*sinks, "sinks");
+        TORCH_CHECK(sinks->numel() == heads, "attention_latent: one sink a head");
+        sp = sinks->data_ptr<float>();
+    }
+    const int* tp = nullptr;
+    int n_tiles = q_start.numel();
+    if (tiles.has_value()) {
+        check_i32(*tiles, "tiles");
+        TORCH_CHECK(tiles->dim() == 2 && tiles->size(1) == 2, "attention_latent: tiles [n, 2]");
+        tp = tiles->data_ptr<int>();
+        n_tiles = tiles->size(0);
+    } else {
+        TORCH_CHECK(q.size(0) >= n_tiles, "attention_latent: a step of single tokens has a token for each sequence");
+    }
+    c10::cuda::CUDAGuard guard(q.device());
+    check_launch(vtb::launch_attention_latent(q.data_ptr(), q.size(1), q_col, out.data_ptr(), out.size(1), out_col, pages.data_ptr(),
+                                              cu_q.data_ptr<int>(), q_start.data_ptr<int>(), block_table.data_ptr<int>(),
+                                              block_table.size(1), tp, n_tiles, pages.size(0), heads, key, v_dim, pages.size(2),
+                                              (float)scale, sp, stream_of(q)), "attention_latent");
+}
+
 void retention_scan(const Tensor& y, int64_t q_col, int64_t k_col, int64_t v_col, const Tensor& decay, double k_scale,
                     c10::optional<Tensor> frequencies, const Tensor& positions, Tensor& state, const Tensor& cu_q, const Tensor& rows,
                     Tensor& o, int64_t heads, int64_t dim, int64_t v_dim, c10::optional<Tensor> status, int64_t most_threads,
@@ -1036,6 +1076,9 @@ PYBIND11_MODULE(TORCH_EXTENSION_NAME, m) {
     m.def("attention_diff", &attention_diff);
     m.def("attention_diff_supports", &vtb::attention_diff_supports);
     m.def("attention_diff_tile_rows", &vtb::attention_diff_tile_rows);
+    m.def("attention_latent", &attention_latent);
+    m.def("attention_latent_supports", &vtb::attention_latent_supports);
+    m.def("attention_latent_tile_rows", &vtb::attention_latent_tile_rows);
     m.def("retention_scan", &retention_scan, py::arg("y"), py::arg("q_col"), py::arg("k_col"), py::arg("v_col"), py::arg("decay"),
           py::arg("k_scale"), py::arg("frequencies"), py::arg("positions"), py::arg("state"), py::arg("cu_q"), py::arg("rows"), py::arg("o"),
           py::arg("heads"), py::arg("dim"), py::arg("v_dim"), py::arg("status") = py::none(), py::arg("most_threads") = 0,

@@ -38,6 +38,7 @@ SOURCES = [
     "attention_general.cu",
     "experts.cu",
     "attention_diff.cu",
+    "attention_latent.cu",
     "latent.cu",
 ]
 HEADERS = ["common.cuh", "kernels.h", "launch.cuh", "tc_common.cuh", "gemm_epilogue.cuh", "attention_mma.cuh", "attention_decode.cuh", "attention_noalloc.h"]

@@ -369,6 +369,28 @@ def attention_differential(y, q_col: int, out, out_col: int, out_scale: float, k
                                          sub_eps=sub_eps)
 
 
+def attention_latent(q, q_col: int, out, out_col: int, pages, ctx, block_table, heads: int, key: int, v_dim: int, scale: float,
+                     sinks=None, status=None):
+    """Softmax attention of the step's tokens over paged rows that all heads share: head h's query [key] stands at
+    q[t, q_col + h * key + :], a cached token's row of ``pages`` [pages, 1, page_size, key] is every head's key and its first
+    ``v_dim`` numbers every head's value; out[t, out_col + h * v_dim + :] = sum_j p_j row_j[:v_dim] with
+    p = softmax_j(scale q . row_j) over the keys j up to the token's position.  ``sinks`` [heads] float32: exp(sinks[h])
+    joins the denominator (no key, no value, not scaled).  bfloat16 at the sizes the tensor-core kernel takes runs that
+    kernel (tiles of 64 rows of (token, head) that share each block of keys; a single token's tile holds its heads);
+    everything else, and all of float32, the plain kernel."""
+    be = backend()
+    if (q.dtype == torch.bfloat16 and ATTENTION_KERNEL in ("auto", "mma") and q_col % 8 == 0 and out_col % 2 == 0
+            and be.attention_latent_supports(int(key), int(v_dim))):
+        singles = ctx.max_q_len == 1 and ctx.n_tokens == ctx.n_seqs
+        rows = be.attention_latent_tile_rows()
+        tiles = None if singles else _attention_tiles(ctx, rows // min(int(heads), rows), q.device)
+        be.attention_latent(q, int(q_col), out, int(out_col), pages, ctx.cu_q, ctx.q_start, block_table, tiles, int(heads), int(key),
+                            int(v_dim), float(scale), sinks)
+        return out
+    return attention_general.__wrapped__(q, q_col, out, out_col, 1.0, pages, pages, ctx, block_table, heads, 1, key, v_dim, None, None,
+                                         scale, status=status, sinks=sinks, values_in_keys=True)
+
+
 def route_experts(logits, top: int, act: torch.Tensor, inter: int, x=None, router=None, weights_by: str = "softmax",
                   scale: float = 1.0) -> torch.Tensor:
     """For every token (row): the ``top`` largest of its router logits [experts] (float32; the lower index among
@@ -864,5 +886,5 @@ def _counted(fn):
 
 
 for _name in ("embedding", "logits_scale_cap", "rmsnorm", "layernorm", "polynorm", "scale_into", "head_norm_gate", "gla_scan", "delta_scan", "retention_scan", "route_experts", "attention_differential", "route_topk", "expert_lists", "gather_picks", "combine_picks",
-              "token_shift", "latent_prepare", "head_matmul", "xielu", "gate_clamp", "attention_prepare", "attention_general", "silu_mul", "rope_store", "linear", "paged_attention", "argmax", "sample"):  # the others count where they launch
+              "token_shift", "latent_prepare", "head_matmul", "attention_latent", "xielu", "gate_clamp", "attention_prepare", "attention_general", "silu_mul", "rope_store", "linear", "paged_attention", "argmax", "sample"):  # the others count where they launch
     globals()[_name] = _counted(globals()[_name])

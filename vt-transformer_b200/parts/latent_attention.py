@@ -100,8 +100,8 @@ class LatentAttention(ProjectedMixer):
         ops.head_matmul(q, 0, self.q_head, self.u, qa, 0, self.key, mode="rotated_tail", tail=s.rot_dim, frequencies=freq, mult=mult,
                         ctx=ctx)
         oc = torch.empty((T, s.heads * s.kv_rank), dtype=y.dtype, device=dev)
-        ops.attention_general(qa, 0, oc, 0, 1.0, pages, pages, ctx, cache.block_table, s.heads, 1, self.key, s.kv_rank, None, None,
-                              s.scale, status=ctx.status, sinks=self.sinks, values_in_keys=True)
+        ops.attention_latent(qa, 0, oc, 0, pages, ctx, cache.block_table, s.heads, self.key, s.kv_rank, s.scale, sinks=self.sinks,
+                             status=ctx.status)
         direct = out_scale == 1.0
         o = out if direct else torch.empty((T, s.heads * s.v_dim), dtype=y.dtype, device=dev)
         ops.head_matmul(oc, 0, s.kv_rank, self.v, o, out_col if direct else 0, s.v_dim, mode="gate" if s.gate else "plain",
