@@ -133,6 +133,40 @@ def test_routing_kernel_with_sigmoid_scores(experts, top):
         assert float((wts.double().cpu().sum(1) - 1.3).abs().max()) <= 1e-5
 
 
+@pytest.mark.parametrize("dtype", [torch.bfloat16, torch.float32])
+@pytest.mark.parametrize("tokens", [5, 150])
+@pytest.mark.parametrize("heads,inner,outer,tail", [(3, 24, 48, 16), (2, 128, 136, 32), (5, 40, 8, 8), (1, 200, 264, 0)])
+def test_products_of_the_heads(dtype, tokens, heads, inner, outer, tail):
+    """out[t, h] = x[t, h] M_h, with the rotated tail copied behind a head's outputs, and with the sigmoid gate: a few tokens
+    (the plain kernel) and many (bfloat16: the tensor cores)."""
+    from vt_transformer_b200 import ops
+    g = torch.Generator().manual_seed(inner + outer)
+    x = torch.randn((tokens, heads, inner + tail), generator=g).to(dtype)
+    m = (torch.randn((heads, inner, outer), generator=g) / math.sqrt(inner)).to(dtype)
+    gate = torch.randn((tokens, 8 + heads * outer), generator=g).to(dtype)
+    freq, mult = plain.rotary_frequencies(max(tail, 2), 300.0, {"factor": 4.0, "original": 16, "fast": 4.0, "slow": 1.0})
+    ctx = helpers.step_context([tokens - 2, 2], [7, 0], DEV)
+    positions = torch.cat([torch.arange(7, 7 + tokens - 2), torch.arange(2)])
+    ref = torch.einsum("thi,hio->tho", x[..., :inner].double(), m.double())
+    tol = 2e-5 if dtype == torch.float32 else 3e-2
+    xd, md = x.view(tokens, -1).to(DEV), m.to(DEV)
+    out = torch.zeros((tokens, 8 + heads * (outer + tail)), dtype=dtype, device=DEV)
+    if tail:
+        ops.head_matmul(xd, 0, inner + tail, md, out, 8, outer + tail, mode="rotated_tail", tail=tail, frequencies=freq.float().to(DEV),
+                        mult=mult, ctx=ctx)
+        turned = plain.rotate_interleaved(x[..., inner:].double(), positions, freq, mult)
+        got = out[:, 8:].double().cpu().view(tokens, heads, outer + tail)
+        assert float((got[..., :outer] - ref).abs().max()) <= tol and float((got[..., outer:] - turned).abs().max()) <= tol
+    else:
+        ops.head_matmul(xd, 0, inner, md, out, 8, outer)
+        assert float((out[:, 8:].double().cpu().view(tokens, heads, outer) - ref).abs().max()) <= tol
+    assert float(out[:, :8].abs().max()) == 0
+    out2 = torch.empty((tokens, heads * outer), dtype=dtype, device=DEV)
+    ops.head_matmul(xd, 0, inner + tail, md, out2, 0, outer, mode="gate", gate=gate.to(DEV), gate_col=8)
+    want = ref * torch.sigmoid(gate[:, 8:].double()).view(tokens, heads, outer)
+    assert float((out2.double().cpu().view(tokens, heads, outer) - want).abs().max()) <= tol
+
+
 @pytest.mark.parametrize("sink", [False, True])
 @pytest.mark.parametrize("heads,key,v_dim,page", [(4, 96, 64, 16), (8, 160, 128, 64), (3, 48, 16, 16), (16, 320, 256, 64), (6, 576, 512, 32),
                                                   (70, 64, 32, 16), (5, 112, 80, 16)])

@@ -9,8 +9,9 @@
 // A tile is 64 rows of (token, head): a block of keys is brought into shared memory once for all of them (two-stage
 // cp.async pipeline), and serves as K in S = Q K^T and, its first DV columns read transposed, as V in O += P V (mma.sync
 // m16n8k16, P rounded to bfloat16).  The queries of the tile stay in shared memory (a row of D numbers does not fit the
-// registers).  Eight warps: a slab of 16 rows has two warps, each forms the slab's scores (both the same, in the same
-// order) and owns one half of the columns of O.  The sink is where the running maximum and sum start: m = sink, l = 1.
+// registers).  Eight warps: a slab of 16 rows has two warps; each forms the slab's scores over one half of the D inner
+// numbers, the two add each other's half through shared memory (so both hold the same scores, maxima and sums), and each
+// owns one half of the columns of O.  The sink is where the running maximum and sum start: m = sink, l = 1.
 // Prompt portions and single tokens run the same kernel (a single token's tile holds its heads).
 #include "attention_mma.cuh"
 #include "common.cuh"
@@ -55,11 +56,15 @@ attention_latent_kernel(const LatentParams p) {
     extern __shared__ __align__(16) unsigned char smem_raw[];
     __nv_bfloat16* qs = reinterpret_cast<__nv_bfloat16*>(smem_raw);   // [64][LD]
     __nv_bfloat16* ks = qs + (size_t)LAT_ROWS * LD;                   // [2 stages][KBL][LD]
+    float4* xch = reinterpret_cast<float4*>(ks + (size_t)2 * KBL * LD); // [8 warps][NJ][32 lanes]: a pair's halves of the scores
 
     pdl_launch();
     pdl_wait();
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31, gq = lane >> 2, tq = lane & 3;
-    const int rg = warp >> 1, col0 = (warp & 1) * HALF;
+    const int rg = warp >> 1, side = warp & 1, col0 = side * HALF;
+    // the pair's warps form the slab's scores over one half of the D inner numbers each and add the other's half
+    const int ks_split = (D / 16 + 1) / 2;
+    const int ks_lo = side ? ks_split : 0, ks_hi = side ? D / 16 : ks_split;
     const int head0 = blockIdx.y * p.heads_per_tile;
     const int nheads = min(p.heads_per_tile, p.heads - head0);
     int seq = blockIdx.x, tok0 = 0;
@@ -164,7 +169,7 @@ attention_latent_kernel(const LatentParams p) {
             const __nv_bfloat16* qrow = qs + (size_t)(row_base + (lane & 7) + ((lane >> 3) & 1) * 8) * LD + (lane >> 4) * 8;
             const int mat = lane >> 3, r = lane & 7;
             const __nv_bfloat16* krow = kst + (size_t)((mat >> 1) * 8 + r) * LD + (mat & 1) * 8;
-            for (int ks_ = 0; ks_ < D / 16; ++ks_) {
+            for (int ks_ = ks_lo; ks_ < ks_hi; ++ks_) {
                 uint32_t qf[4];
                 ldmatrix_x4(qf, qrow + ks_ * 16);
 #pragma unroll
@@ -174,6 +179,18 @@ attention_latent_kernel(const LatentParams p) {
                     mma_bf16(s[j], qf, kf[0], kf[1]);
                     mma_bf16(s[j + 1], qf, kf[2], kf[3]);
                 }
+            }
+        }
+        {
+            float4* mine = xch + (size_t)warp * NJ * 32 + lane;
+#pragma unroll
+            for (int j = 0; j < NJ; ++j) mine[j * 32] = make_float4(s[j][0], s[j][1], s[j][2], s[j][3]);
+            asm volatile("bar.sync %0, 64;\n" ::"r"(1 + rg) : "memory");          // the two warps of the slab
+            const float4* theirs = xch + (size_t)(warp ^ 1) * NJ * 32 + lane;
+#pragma unroll
+            for (int j = 0; j < NJ; ++j) {                                        // a + b = b + a: both warps hold the same sums
+                const float4 t = theirs[j * 32];
+                s[j][0] += t.x; s[j][1] += t.y; s[j][2] += t.z; s[j][3] += t.w;
             }
         }
         // mask, running maximum and sum (log2 domain)
@@ -267,7 +284,7 @@ attention_latent_kernel(const LatentParams p) {
 template <int DVT, int KBL>
 cudaError_t launch_latent_as(const LatentParams& p, int n_tiles, int head_groups, cudaStream_t stream) {
     static std::atomic<unsigned long long> done{0};
-    const int bytes = (LAT_ROWS + 2 * KBL) * (p.D + 8) * 2;
+    const int bytes = (LAT_ROWS + 2 * KBL) * (p.D + 8) * 2 + 8 * (KBL / 8) * 32 * 16;
     cudaError_t e = allow_dynamic_smem(attention_latent_kernel<DVT, KBL>, 200 * 1024, done);
     if (e != cudaSuccess) return e;
     return launch(attention_latent_kernel<DVT, KBL>, dim3(n_tiles, head_groups), dim3(256), bytes, stream, p);
@@ -282,7 +299,7 @@ int attention_latent_tile_rows() { return LAT_ROWS; }
 bool attention_latent_supports(int key, int v_dim) {
     if (key % 16 || v_dim % 16 || v_dim < 16 || v_dim > 512 || v_dim > key) return false;
     const int kbl = v_dim > 256 ? 32 : 64;
-    return (LAT_ROWS + 2 * kbl) * (key + 8) * 2 <= 200 * 1024;
+    return (LAT_ROWS + 2 * kbl) * (key + 8) * 2 + 8 * (kbl / 8) * 32 * 16 <= 200 * 1024;
 }
 
 cudaError_t launch_attention_latent(const void* q, int q_stride, int q_col, void* out, int out_stride, int out_col, const void* pages,

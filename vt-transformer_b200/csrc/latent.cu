@@ -9,6 +9,7 @@
 // The queries are therefore taken into the latent's space once a token (`head_matmul` with U_h, mode 1 also rotates
 // q_r), the attention runs over the pages' rows as they lie (every head reads the same keys; a value is the first
 // kv_rank numbers of its key's row), and the result is taken through V_h (`head_matmul` again, with the output gate).
+#include "attention_mma.cuh"
 #include "common.cuh"
 #include "kernels.h"
 #include "launch.cuh"
@@ -228,6 +229,104 @@ head_matmul_kernel(const T* __restrict__ x, int x_stride, int x_col, int x_head,
     }
 }
 
+// The same product on the tensor cores (bfloat16, 32-bit sums, one rounding), for steps with many tokens: a CTA forms 64
+// tokens x 128 outputs of one head, its four warps 16 tokens each; x and M_h come in slices of 32 inner numbers through a
+// two-stage cp.async pipeline (mma.sync m16n8k16; M_h's slice [inner][outer] is read transposed by ldmatrix).
+constexpr int kHmRows = 64, kHmCols = 128, kHmInner = 32;
+
+__global__ void __launch_bounds__(128)
+head_matmul_mma_kernel(const __nv_bfloat16* __restrict__ x, int x_stride, int x_col, int x_head, const __nv_bfloat16* __restrict__ m,
+                       int inner, int outer, __nv_bfloat16* __restrict__ out, int out_stride, int out_col, int out_head, int n_tokens,
+                       int mode, int tail, const float* __restrict__ freq, int half, float mult, const int* __restrict__ positions,
+                       const int* __restrict__ token_seq, const __nv_bfloat16* __restrict__ gate, int gate_stride, int gate_col) {
+    constexpr int LA = kHmInner + 8, LB = kHmCols + 8;
+    __shared__ __align__(16) __nv_bfloat16 as[2][kHmRows][LA];
+    __shared__ __align__(16) __nv_bfloat16 bs[2][kHmInner][LB];
+    pdl_launch();
+    pdl_wait();
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31, gq = lane >> 2, tq = lane & 3;
+    const int t0 = blockIdx.x * kHmRows, h = blockIdx.y, n0 = blockIdx.z * kHmCols;
+    const int n = min(kHmRows, n_tokens - t0);
+    const __nv_bfloat16* xh = x + (size_t)t0 * x_stride + x_col + (size_t)h * x_head;
+    const __nv_bfloat16* mh = m + (size_t)h * inner * outer + n0;
+    auto load_slice = [&](int k0, int stage) {
+        for (int c = threadIdx.x; c < kHmRows * (kHmInner / 8); c += 128) {
+            const int r = c / (kHmInner / 8), piece = c % (kHmInner / 8);
+            const bool ok = r < n && k0 + piece * 8 < inner;
+            cp_async16(&as[stage][r][piece * 8], xh + (ok ? (size_t)r * x_stride + k0 + piece * 8 : 0), ok);
+        }
+        for (int c = threadIdx.x; c < kHmInner * (kHmCols / 8); c += 128) {
+            const int r = c / (kHmCols / 8), piece = c % (kHmCols / 8);
+            const bool ok = k0 + r < inner && n0 + piece * 8 < outer;
+            cp_async16(&bs[stage][r][piece * 8], mh + (ok ? (size_t)(k0 + r) * outer + piece * 8 : 0), ok);
+        }
+    };
+    float acc[kHmCols / 8][4];
+#pragma unroll
+    for (int i = 0; i < kHmCols / 8; ++i) acc[i][0] = acc[i][1] = acc[i][2] = acc[i][3] = 0.f;
+    const int slices = (inner + kHmInner - 1) / kHmInner;
+    load_slice(0, 0);
+    cp_async_commit();
+    for (int sl = 0; sl < slices; ++sl) {
+        const int stage = sl & 1;
+        if (sl + 1 < slices) load_slice((sl + 1) * kHmInner, stage ^ 1);
+        cp_async_commit();
+        cp_async_wait<1>();
+        __syncthreads();
+#pragma unroll
+        for (int kk = 0; kk < kHmInner / 16; ++kk) {
+            uint32_t af[4];
+            ldmatrix_x4(af, &as[stage][warp * 16 + (lane & 7) + ((lane >> 3) & 1) * 8][kk * 16 + (lane >> 4) * 8]);
+            const int mat = lane >> 3, r = lane & 7;
+#pragma unroll
+            for (int dn = 0; dn < kHmCols / 16; ++dn) {
+                if (n0 + dn * 16 < outer) {
+                    uint32_t bf[4];
+                    ldmatrix_x4_trans(bf, &bs[stage][kk * 16 + (mat & 1) * 8 + r][dn * 16 + (mat >> 1) * 8]);
+                    mma_bf16(acc[2 * dn], af, bf[0], bf[1]);
+                    mma_bf16(acc[2 * dn + 1], af, bf[2], bf[3]);
+                }
+            }
+        }
+        __syncthreads();
+    }
+#pragma unroll
+    for (int i = 0; i < 2; ++i) {
+        const int tk = warp * 16 + gq + 8 * i;
+        if (tk >= n) continue;
+        __nv_bfloat16* op = out + (size_t)(t0 + tk) * out_stride + out_col + (size_t)h * out_head;
+        const __nv_bfloat16* gp = (mode == 2 && gate != nullptr) ? gate + (size_t)(t0 + tk) * gate_stride + gate_col + (size_t)h * outer : nullptr;
+#pragma unroll
+        for (int nt = 0; nt < kHmCols / 8; ++nt) {
+            const int j = n0 + nt * 8 + 2 * tq;
+            if (j >= outer) continue;
+            float v0 = acc[nt][2 * i], v1 = acc[nt][2 * i + 1];
+            if (gp) {
+                v0 *= 1.f / (1.f + expf(-__bfloat162float(gp[j])));
+                v1 *= 1.f / (1.f + expf(-__bfloat162float(gp[j + 1])));
+            }
+            *reinterpret_cast<uint32_t*>(op + j) = pack_bf16(v0, v1);
+        }
+    }
+    if (mode != 1 || blockIdx.z != 0) return;
+    // the head's rotated part, behind its outputs
+    for (int e = threadIdx.x; e < n * tail; e += 128) {
+        const int tk = e / tail, i = e % tail, t = t0 + tk;
+        const __nv_bfloat16* src = x + (size_t)t * x_stride + x_col + h * x_head + inner;
+        float v = __bfloat162float(src[i]);
+        if (i < 2 * half && token_seq[t] >= 0) {
+            float a, b;
+            const int pair = i >> 1;
+            turn_pair(__bfloat162float(src[2 * pair]), __bfloat162float(src[2 * pair + 1]), positions[t], freq[pair], mult, a, b);
+            v = (i & 1) ? b : a;
+        }
+        out[(size_t)t * out_stride + out_col + h * out_head + outer + i] = __float2bfloat16_rn(v);
+    }
+}
+
+// from how many tokens on a step's products of the heads run on the tensor cores (below, M_h's bytes bound the time)
+constexpr int kHmMinTokens = 32;
+
 cudaError_t launch_head_matmul(int dtype, int m_dtype, const void* x, int x_stride, int x_col, int x_head, const void* m, int heads,
                                int inner, int outer, void* out, int out_stride, int out_col, int out_head, int n_tokens, int mode,
                                int tail, const float* freq, int half, float mult, const int* positions, const int* token_seq,
@@ -235,6 +334,14 @@ cudaError_t launch_head_matmul(int dtype, int m_dtype, const void* x, int x_stri
     if (n_tokens == 0 || heads == 0) return cudaSuccess;
     if (2 * half > tail || (mode == 1 && half > 0 && (freq == nullptr || positions == nullptr || token_seq == nullptr)))
         return cudaErrorInvalidValue;
+    if (dtype == kBF16 && m_dtype == kBF16 && n_tokens >= kHmMinTokens && inner % 8 == 0 && outer % 8 == 0 && x_stride % 8 == 0 &&
+        x_col % 8 == 0 && x_head % 8 == 0 && out_stride % 2 == 0 && out_col % 2 == 0 && out_head % 2 == 0 &&
+        ((uintptr_t)x & 15) == 0 && ((uintptr_t)m & 15) == 0 && ((uintptr_t)out & 3) == 0) {
+        const dim3 grid_mma((n_tokens + kHmRows - 1) / kHmRows, heads, (outer + kHmCols - 1) / kHmCols);
+        return launch(head_matmul_mma_kernel, grid_mma, 128, 0, stream, (const __nv_bfloat16*)x, x_stride, x_col, x_head,
+                      (const __nv_bfloat16*)m, inner, outer, (__nv_bfloat16*)out, out_stride, out_col, out_head, n_tokens, mode, tail, freq,
+                      half, mult, positions, token_seq, (const __nv_bfloat16*)gate, gate_stride, gate_col);
+    }
     const size_t bytes = (size_t)inner * kHeadTokens * sizeof(float);
     if (bytes > 48 * 1024) return cudaErrorInvalidValue;                     // inner sizes up to 1,536
     const dim3 grid((n_tokens + kHeadTokens - 1) / kHeadTokens, heads, (outer + kHeadCols - 1) / kHeadCols);
