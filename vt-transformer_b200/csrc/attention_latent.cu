@@ -37,6 +37,10 @@ struct LatentParams {
     float scale_log2;                // scale * log2(e)
     const float* sinks;              // [heads] or null
     int tokens_per_tile, heads_per_tile;
+    // a step of single tokens may cut every sequence's keys into n_splits runs of blocks, a CTA each (blockIdx.z): the runs
+    // leave their unnormalised sums, maxima and sums in part [n_splits, tokens, heads, DV + 2] and a second kernel merges them
+    int n_splits, n_tokens;
+    float* part;
 };
 
 namespace {
@@ -91,6 +95,12 @@ attention_latent_kernel(const LatentParams p) {
     const int pos_lo = p.q_start[seq] + tok0, pos_hi = pos_lo + ntok - 1;
     const int key_hi = pos_hi + 1;
     const int nblk = (key_hi + KBL - 1) / KBL;
+    int blk_lo = 0, blk_hi = nblk;
+    if (p.n_splits > 1) {
+        const int per = (nblk + p.n_splits - 1) / p.n_splits;
+        blk_lo = min(nblk, (int)blockIdx.z * per);
+        blk_hi = min(nblk, blk_lo + per);
+    }
 
     // the two rows of this thread
     int pos[2], tok[2], head[2];
@@ -136,7 +146,7 @@ attention_latent_kernel(const LatentParams p) {
     // the sink is the first term of the softmax: the maximum starts at it and the sum at one (held by one of the four
     // lanes that share a row: the lanes' sums are added at the end)
     float mrow[2] = {-INFINITY, -INFINITY}, lrow[2] = {0.f, 0.f};
-    if (p.sinks) {
+    if (p.sinks && blockIdx.z == 0) {
 #pragma unroll
         for (int i = 0; i < 2; ++i) {
             if (valid[i]) {
@@ -146,11 +156,11 @@ attention_latent_kernel(const LatentParams p) {
         }
     }
 
-    load_block(0, 0);
+    if (blk_lo < blk_hi) load_block(blk_lo, 0);
     cp_async_commit();
-    for (int blk = 0; blk < nblk; ++blk) {
-        const int stage = blk & 1;
-        if (blk + 1 < nblk) load_block(blk + 1, stage ^ 1);
+    for (int blk = blk_lo; blk < blk_hi; ++blk) {
+        const int stage = (blk - blk_lo) & 1;
+        if (blk + 1 < blk_hi) load_block(blk + 1, stage ^ 1);
         cp_async_commit();
         cp_async_wait<1>();
         __syncthreads();
@@ -271,6 +281,19 @@ attention_latent_kernel(const LatentParams p) {
         lrow[i] += __shfl_xor_sync(0xffffffffu, lrow[i], 1);
         lrow[i] += __shfl_xor_sync(0xffffffffu, lrow[i], 2);
         if (!valid[i]) continue;
+        if (p.n_splits > 1) {
+            float* dst = p.part + (((size_t)blockIdx.z * p.n_tokens + tok[i]) * p.heads + head[i]) * (DV + 2);
+#pragma unroll
+            for (int nt = 0; nt < 2 * ND; ++nt) {
+                const int col = col0 + nt * 8 + 2 * tq;
+                if (col < DV) *reinterpret_cast<float2*>(dst + col) = make_float2(o[nt][2 * i], o[nt][2 * i + 1]);
+            }
+            if (side == 0 && tq == 0) {
+                dst[DV] = mrow[i];
+                dst[DV + 1] = lrow[i];
+            }
+            continue;
+        }
         const float inv = lrow[i] > 0.f ? 1.f / lrow[i] : 0.f;
         __nv_bfloat16* op = p.out + (size_t)tok[i] * p.out_stride + p.out_col + (size_t)head[i] * DV;
 #pragma unroll
@@ -281,13 +304,45 @@ attention_latent_kernel(const LatentParams p) {
     }
 }
 
+// The runs of a sequence's keys meet: out = sum_s o_s 2^(m_s - m) / sum_s l_s 2^(m_s - m), m the largest maximum of the
+// runs that saw a key (or hold the sink), in the order of the runs.  A CTA a (token, head).
+__global__ void __launch_bounds__(128)
+attention_latent_merge_kernel(const float* __restrict__ part, int n_splits, int n_tokens, int heads, int DV, const int* __restrict__ cu_q,
+                              __nv_bfloat16* __restrict__ out, int out_stride, int out_col) {
+    pdl_launch();
+    pdl_wait();
+    const int t = blockIdx.x, h = blockIdx.y;
+    if (cu_q[t + 1] - cu_q[t] <= 0) return;            // a padding token: its row was cleared
+    const size_t stride = (size_t)n_tokens * heads * (DV + 2);
+    const float* src = part + ((size_t)t * heads + h) * (DV + 2);
+    float w[16];
+    float m = -INFINITY, l = 0.f;
+    for (int s = 0; s < n_splits; ++s)
+        if (src[s * stride + DV + 1] > 0.f) m = fmaxf(m, src[s * stride + DV]);
+    for (int s = 0; s < n_splits; ++s) {
+        const float ls = src[s * stride + DV + 1];
+        w[s] = ls > 0.f ? fast_exp2(src[s * stride + DV] - m) : 0.f;
+        l += ls * w[s];
+    }
+    const float inv = l > 0.f ? 1.f / l : 0.f;
+    for (int c = threadIdx.x; c < DV; c += 128) {
+        float acc = 0.f;
+        for (int s = 0; s < n_splits; ++s)
+            if (w[s] > 0.f) acc = fmaf(src[s * stride + c], w[s], acc);
+        out[(size_t)t * out_stride + out_col + (size_t)h * DV + c] = __float2bfloat16_rn(acc * inv);
+    }
+}
+
 template <int DVT, int KBL>
 cudaError_t launch_latent_as(const LatentParams& p, int n_tiles, int head_groups, cudaStream_t stream) {
     static std::atomic<unsigned long long> done{0};
     const int bytes = (LAT_ROWS + 2 * KBL) * (p.D + 8) * 2 + 8 * (KBL / 8) * 32 * 16;
     cudaError_t e = allow_dynamic_smem(attention_latent_kernel<DVT, KBL>, 200 * 1024, done);
     if (e != cudaSuccess) return e;
-    return launch(attention_latent_kernel<DVT, KBL>, dim3(n_tiles, head_groups), dim3(256), bytes, stream, p);
+    e = launch(attention_latent_kernel<DVT, KBL>, dim3(n_tiles, head_groups, p.n_splits), dim3(256), bytes, stream, p);
+    if (e != cudaSuccess || p.n_splits <= 1) return e;
+    return launch(attention_latent_merge_kernel, dim3(n_tiles, p.heads), dim3(128), 0, stream, (const float*)p.part, p.n_splits, p.n_tokens,
+                  p.heads, p.DV, p.cu_q, p.out, p.out_stride, p.out_col);
 }
 
 }  // namespace
@@ -305,13 +360,14 @@ bool attention_latent_supports(int key, int v_dim) {
 cudaError_t launch_attention_latent(const void* q, int q_stride, int q_col, void* out, int out_stride, int out_col, const void* pages,
                                     const int* cu_q, const int* q_start, const int* block_table, int table_stride, const int* tiles,
                                     int n_tiles, int n_pages, int heads, int key, int v_dim, int page_size, float scale,
-                                    const float* sinks, cudaStream_t stream) {
+                                    const float* sinks, int n_splits, float* part, int n_tokens, cudaStream_t stream) {
     if (n_tiles == 0) return cudaSuccess;
     if (!attention_latent_supports(key, v_dim)) return cudaErrorInvalidValue;
+    if (n_splits < 1 || n_splits > 16 || (n_splits > 1 && (tiles != nullptr || part == nullptr))) return cudaErrorInvalidValue;
     const int hpt = heads < LAT_ROWS ? heads : LAT_ROWS;
     LatentParams p = {(const __nv_bfloat16*)q, q_stride, q_col, (__nv_bfloat16*)out, out_stride, out_col, (const __nv_bfloat16*)pages,
                       cu_q, q_start, block_table, table_stride, reinterpret_cast<const int2*>(tiles), n_pages, heads, page_size, key,
-                      v_dim, scale * 1.4426950408889634f, sinks, LAT_ROWS / hpt, hpt};
+                      v_dim, scale * 1.4426950408889634f, sinks, LAT_ROWS / hpt, hpt, n_splits, n_tokens, part};
     const int groups = (heads + hpt - 1) / hpt;
     if (v_dim <= 64) return launch_latent_as<64, 64>(p, n_tiles, groups, stream);
     if (v_dim <= 128) return launch_latent_as<128, 64>(p, n_tiles, groups, stream);

@@ -344,7 +344,7 @@ void attention_diff(const Tensor& y, int64_t q_col, Tensor& out, int64_t out_col
 
 void attention_latent(const Tensor& q, int64_t q_col, Tensor& out, int64_t out_col, const Tensor& pages, const Tensor& cu_q,
                       const Tensor& q_start, const Tensor& block_table, c10::optional<Tensor> tiles, int64_t heads, int64_t key,
-                      int64_t v_dim, double scale, c10::optional<Tensor> sinks) {
+                      int64_t v_dim, double scale, c10::optional<Tensor> sinks, c10::optional<Tensor> part) {
     check_cuda(q, "q"); check_cuda(out, "out"); check_cuda(pages, "pages");
     check_i32(cu_q, "cu_q"); check_i32(q_start, "q_start"); check_i32(block_table, "block_table");
     TORCH_CHECK(q.scalar_type() == torch::kBFloat16 && out.scalar_type() == torch::kBFloat16 && pages.scalar_type() == torch::kBFloat16,
@@ -375,11 +375,21 @@ void attention_latent(const Tensor& q, int64_t q_col, Tensor& out, int64_t out_c
     } else {
         TORCH_CHECK(q.size(0) >= n_tiles, "attention_latent: a step of single tokens has a token for each sequence");
     }
+    float* pp = nullptr;
+    int n_splits = 1;
+    if (part.has_value()) {
+        check_f32(*part, "part");
+        TORCH_CHECK(!tiles.has_value() && part->dim() == 4 && part->size(0) >= 1 && part->size(0) <= 16 && part->size(1) == q.size(0) &&
+                    part->size(2) == heads && part->size(3) == v_dim + 2 && part->is_contiguous(),
+                    "attention_latent: part [runs <= 16, tokens, heads, v_dim + 2], with a step of single tokens");
+        pp = part->data_ptr<float>();
+        n_splits = part->size(0);
+    }
     c10::cuda::CUDAGuard guard(q.device());
     check_launch(vtb::launch_attention_latent(q.data_ptr(), q.size(1), q_col, out.data_ptr(), out.size(1), out_col, pages.data_ptr(),
                                               cu_q.data_ptr<int>(), q_start.data_ptr<int>(), block_table.data_ptr<int>(),
                                               block_table.size(1), tp, n_tiles, pages.size(0), heads, key, v_dim, pages.size(2),
-                                              (float)scale, sp, stream_of(q)), "attention_latent");
+                                              (float)scale, sp, n_splits, pp, q.size(0), stream_of(q)), "attention_latent");
 }
 
 void retention_scan(const Tensor& y, int64_t q_col, int64_t k_col, int64_t v_col, const Tensor& decay, double k_scale,

@@ -82,13 +82,15 @@ cudaError_t launch_attention_general(int dtype, const void* y, int stride, int q
 // Attention over paged rows that all heads share (attention_latent.cu), bfloat16 on the tensor cores: head h's query
 // [key] at q_col + h * key of q; a row's first v_dim numbers are its value; out[t, out_col + h * v_dim + :].  sinks [heads]
 // or null: exp(sink_h) joins the softmax's denominator.  tiles [n_tiles, 2] (sequence, first token), or null for a step
-// of single tokens; a tile holds attention_latent_tile_rows() / min(heads, that) tokens.
+// of single tokens; a tile holds attention_latent_tile_rows() / min(heads, that) tokens.  A step of single tokens may cut every
+// sequence's keys into n_splits (up to 16) runs with a CTA each, merged by a second kernel through part
+// [n_splits, n_tokens, heads, v_dim + 2] float32.
 bool attention_latent_supports(int key, int v_dim);
 int attention_latent_tile_rows();
 cudaError_t launch_attention_latent(const void* q, int q_stride, int q_col, void* out, int out_stride, int out_col, const void* pages,
                                     const int* cu_q, const int* q_start, const int* block_table, int table_stride, const int* tiles,
                                     int n_tiles, int n_pages, int heads, int key, int v_dim, int page_size, float scale,
-                                    const float* sinks, cudaStream_t stream);
+                                    const float* sinks, int n_splits, float* part, int n_tokens, cudaStream_t stream);
 
 // Differential attention on the tensor cores (attention_diff.cu), bfloat16: the two maps of attention_general with
 // maps 2, for the sizes that attention_diff_supports names.  tiles [n_tiles, 2] (sequence, first token), or null for a

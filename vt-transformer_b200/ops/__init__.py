@@ -369,6 +369,10 @@ def attention_differential(y, q_col: int, out, out_col: int, out_scale: float, k
                                          sub_eps=sub_eps)
 
 
+LATENT_TARGET_CTAS = 296     # CTAs that a step of single tokens aims at (two for each SM), and the most runs a sequence is cut into
+LATENT_MAX_RUNS = 16
+
+
 def attention_latent(q, q_col: int, out, out_col: int, pages, ctx, block_table, heads: int, key: int, v_dim: int, scale: float,
                      sinks=None, status=None):
     """Softmax attention of the step's tokens over paged rows that all heads share: head h's query [key] stands at
@@ -384,8 +388,15 @@ def attention_latent(q, q_col: int, out, out_col: int, pages, ctx, block_table, 
         singles = ctx.max_q_len == 1 and ctx.n_tokens == ctx.n_seqs
         rows = be.attention_latent_tile_rows()
         tiles = None if singles else _attention_tiles(ctx, rows // min(int(heads), rows), q.device)
+        part = None
+        if singles:
+            # few sequences leave most SMs without a CTA: every sequence's keys are cut into runs, a CTA each
+            ctas = ctx.n_seqs * -(-int(heads) // rows)
+            runs = min(LATENT_MAX_RUNS, max(1, LATENT_TARGET_CTAS // ctas))
+            if runs > 1:
+                part = torch.empty((runs, q.shape[0], int(heads), int(v_dim) + 2), dtype=torch.float32, device=q.device)
         be.attention_latent(q, int(q_col), out, int(out_col), pages, ctx.cu_q, ctx.q_start, block_table, tiles, int(heads), int(key),
-                            int(v_dim), float(scale), sinks)
+                            int(v_dim), float(scale), sinks, part)
         return out
     return attention_general.__wrapped__(q, q_col, out, out_col, 1.0, pages, pages, ctx, block_table, heads, 1, key, v_dim, None, None,
                                          scale, status=status, sinks=sinks, values_in_keys=True)
