@@ -111,6 +111,27 @@ def test_activation_kernels(dtype):
         assert float((out.double().cpu() - ref).abs().max()) <= (2e-6 if dtype == torch.float32 else 3e-2)
 
 
+@pytest.mark.parametrize("dtype", [torch.bfloat16, torch.float32])
+@pytest.mark.parametrize("heads,v_dim", [(1, 84), (1, 1100), (2, 2048), (3, 40)])
+def test_heads_normed_together_and_gated(dtype, heads, v_dim):
+    """The heads' results normed as one vector with a weight a channel, times sigmoid(gate): narrow heads (a warp each) and
+    wide ones (a CTA each); the row of a padding token becomes zero."""
+    from vt_transformer_b200 import ops
+    g = torch.Generator().manual_seed(v_dim)
+    T = 6
+    o = torch.randn((T, heads * v_dim), generator=g) * 3
+    y = torch.randn((T, 16 + heads * v_dim), generator=g).to(dtype)
+    w = 1 + 0.2 * torch.randn(heads * v_dim, generator=g)
+    seq = torch.tensor([0, 0, 1, -1, 2, 2], dtype=torch.int32)
+    out = torch.full((T, 8 + heads * v_dim), 5.0, dtype=dtype, device=DEV)
+    ops.head_norm_gate(o.to(DEV), y.to(DEV), 16, w.to(DEV), True, 1e-5, "sigmoid", out, 8, 1.0, heads, v_dim, token_seq=seq.to(DEV))
+    ref = torch.cat([plain.rms_norm(o[:, h * v_dim:(h + 1) * v_dim].double(), w[h * v_dim:(h + 1) * v_dim].double(), 1e-5) for h in range(heads)], dim=1)
+    ref = ref * torch.sigmoid(y[:, 16:].double())
+    ref[3] = 0
+    assert float((out[:, 8:].double().cpu() - ref).abs().max()) <= (2e-5 if dtype == torch.float32 else 4e-2)
+    assert float((out[:, :8].float().cpu() - 5.0).abs().max()) == 0
+
+
 @pytest.mark.parametrize("experts,top", [(5, 2), (1, 1), (40, 40), (130, 7), (3, 1)])
 def test_routing_kernel_with_sigmoid_scores(experts, top):
     """Rows that point along router rows, so that no choice is a close call: the picks are those of the plain routing and

@@ -582,11 +582,54 @@ head_norm_gate_kernel(const float* __restrict__ o, const T* __restrict__ y, int 
     }
 }
 
+// The same for heads of many values (heads normed together are one head as wide as all of them): a CTA a (token, head),
+// its warps' sums of squares added in the order of the warps.
+template <typename T>
+__global__ void __launch_bounds__(256)
+head_norm_gate_wide_kernel(const float* __restrict__ o, const T* __restrict__ y, int y_stride, int gate_col,
+                           const float* __restrict__ weight, int weight_per_channel, float eps, int act, T* __restrict__ out,
+                           int out_stride, int out_col, float out_scale, const int* __restrict__ token_seq, int heads, int v_dim) {
+    __shared__ float sums[8];
+    pdl_launch();
+    pdl_wait();
+    const int t = blockIdx.x / heads, h = blockIdx.x % heads;
+    T* dst = out + (size_t)t * out_stride + out_col + h * v_dim;
+    if (token_seq != nullptr && token_seq[t] < 0) {     // padding: nothing ran for this token
+        for (int i = threadIdx.x; i < v_dim; i += 256) dst[i] = from_float<T>(0.f);
+        return;
+    }
+    const float* src = o + ((size_t)t * heads + h) * v_dim;
+    float ss = 0.f;
+    for (int i = threadIdx.x; i < v_dim; i += 256) ss = fmaf(src[i], src[i], ss);
+    ss = warp_sum(ss);
+    if ((threadIdx.x & 31) == 0) sums[threadIdx.x >> 5] = ss;
+    __syncthreads();
+    float total = 0.f;
+#pragma unroll
+    for (int k = 0; k < 8; ++k) total += sums[k];
+    const float r = rsqrtf(total / (float)v_dim + eps) * out_scale;
+    const T* gate = y + (size_t)t * y_stride + gate_col + h * v_dim;
+    const float* w = weight + (weight_per_channel ? h * v_dim : 0);
+    for (int i = threadIdx.x; i < v_dim; i += 256) {
+        const float z = to_float(gate[i]);
+        const float sg = 1.f / (1.f + expf(-z));
+        dst[i] = from_float<T>(src[i] * r * w[i] * (act == 0 ? z * sg : sg));
+    }
+}
+
 cudaError_t launch_head_norm_gate(int dtype, const float* o, const void* y, int y_stride, int gate_col, const float* weight,
                                   int weight_per_channel, float eps, int act, void* out, int out_stride, int out_col,
                                   float out_scale, const int* token_seq, int n_tokens, int heads, int v_dim, cudaStream_t stream) {
     const long long pairs = (long long)n_tokens * heads;
     if (pairs == 0) return cudaSuccess;
+    if (v_dim >= 1024) {
+        if (dtype == kBF16)
+            return launch(head_norm_gate_wide_kernel<__nv_bfloat16>, (int)pairs, 256, 0, stream, o, (const __nv_bfloat16*)y, y_stride,
+                          gate_col, weight, weight_per_channel, eps, act, (__nv_bfloat16*)out, out_stride, out_col, out_scale, token_seq,
+                          heads, v_dim);
+        return launch(head_norm_gate_wide_kernel<float>, (int)pairs, 256, 0, stream, o, (const float*)y, y_stride, gate_col, weight,
+                      weight_per_channel, eps, act, (float*)out, out_stride, out_col, out_scale, token_seq, heads, v_dim);
+    }
     const int blocks = (int)((pairs + 3) / 4);
     if (dtype == kBF16)
         return launch(head_norm_gate_kernel<__nv_bfloat16>, blocks, 128, 0, stream, o, (const __nv_bfloat16*)y, y_stride, gate_col,
