@@ -189,7 +189,7 @@ def test_products_of_the_heads(dtype, tokens, heads, inner, outer, tail):
 
 
 @pytest.mark.parametrize("sink", [False, True])
-@pytest.mark.parametrize("heads,key,v_dim,page", [(4, 96, 64, 16), (8, 160, 128, 64), (3, 48, 16, 16), (16, 320, 256, 64), (6, 576, 512, 32),
+@pytest.mark.parametrize("heads,key,v_dim,page", [(5, 80, 64, 16), (6, 176, 128, 64), (3, 48, 16, 16), (16, 320, 256, 64), (6, 576, 512, 32),
                                                   (70, 64, 32, 16), (5, 112, 80, 16)])
 def test_latent_attention_kernel_on_the_tensor_cores(heads, key, v_dim, page, sink):
     """Rows that all heads share, their first numbers the values: a sequence that goes on from 37 cached tokens beside one
