@@ -55,8 +55,8 @@ def _model(vocab, width, layers, groups=1, alpha=1.0, eps=1e-5):
 # Configurations that differ from one another in every size and constant: values wider and narrower than the plain key
 # part and as wide, rotated parts from 4 to 32 dimensions, latents of the queries wider and narrower than the keys' and
 # of a size that is no multiple of 8, one head, with and without the ramp over the rotation's frequencies on either
-# kind of attention (pairs on both sides of the ramp and inside it), a scale that is not 1 / sqrt(head), norms in 1, 2
-# and 4 groups, a stream scale of 1 and others, decays of exactly 1 and far below, dense feed-forwards whose inner size
+# kind of attention (pairs on both sides of the ramp and inside it), a scale that is not 1 / sqrt(head), norms in 1 to 6
+# groups (also groups of 12 values, no multiple of 8), a stream scale of 1 and others, decays of exactly 1 and far below, dense feed-forwards whose inner size
 # is no multiple of 8, experts with top of 1 and of all, with and without the shared expert and with a clamp of its own,
 # layers without a feed-forward, layers that use an earlier layer's weights (of each kind of mixer, more than once).
 _M1 = _moe(5, 2, 2.0, 20, 1.5, shared=(36, 3.0))
@@ -74,7 +74,7 @@ CONFIGS: Dict[str, dict] = {
                              _lat(6, 16, 24, 72, 64, 40, 0.25, 1e6, mlp=_moe(3, 2, 1.7, 12, 4.0)),
                              _lig(2, 72, 16, [0.99, 0.5], mlp=_dense(52), weights_of=1),
                              _lig(2, 72, 16, [0.99, 0.5], mlp=_dense(52), weights_of=3)],
-                   groups=1, alpha=1.0, eps=1e-6),
+                   groups=6, alpha=1.0, eps=1e-6),
     "latent_alone": _model(128, 48, [_lat(4, 16, 8, 24, 24, 32, 0.22, 777.0, scaling=(6.0, 32, 8.0, 1.0))], groups=2, alpha=1.6),
     "latent2_alone": _model(128, 48, [_lat(3, 8, 16, 16, 40, 24, 0.27, 300.0, second=True)], groups=3, alpha=0.7),
     "lightning_alone": _model(128, 48, [_lig(3, 20, 28, [0.8, 0.95, 0.99])], groups=1, alpha=1.3),

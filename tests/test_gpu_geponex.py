@@ -67,7 +67,7 @@ def test_token_shift_kernel_carries_the_row_before(dtype, width):
 
 
 @pytest.mark.parametrize("dtype", [torch.bfloat16, torch.float32])
-@pytest.mark.parametrize("width,groups", [(48, 1), (48, 3), (200, 5), (4096, 2), (4104, 1)])
+@pytest.mark.parametrize("width,groups", [(48, 1), (48, 3), (200, 5), (4096, 2), (4104, 1), (72, 6), (200, 50)])
 def test_norm_kernel_in_groups_after_the_scaled_sum(dtype, width, groups):
     """x <- norm(a x + delta) in groups, the unrounded result back into the stream and a rounded copy for the next part."""
     from vt_transformer_b200 import ops

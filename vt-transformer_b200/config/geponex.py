@@ -124,9 +124,8 @@ class GeponexConfig(ModelConfig):
         if self.width % 8:
             raise ConfigError(f"{where}: 'width' {self.width} is not supported: the matrix kernels read rows in "
                               f"16-byte pieces, so it must be a multiple of 8")
-        if self.width % self.norm_groups or (self.width // self.norm_groups) % 8:
-            raise ConfigError(f"{where}: norm 'groups' {self.norm_groups} must cut 'width' {self.width} into equal parts of "
-                              f"a multiple of 8 values")
+        if self.width % self.norm_groups:
+            raise ConfigError(f"{where}: norm 'groups' {self.norm_groups} must cut 'width' {self.width} into equal parts")
         for i, layer in enumerate(self.layers):
             at = f"{where}: layers[{i}]"
             if layer.weights_of is not None:

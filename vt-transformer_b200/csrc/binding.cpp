@@ -72,8 +72,9 @@ void norm_rows(bool center, Tensor& x, c10::optional<Tensor> delta, const Tensor
     TORCH_CHECK(x.dim() == 2, "rmsnorm: x must be 2-d");
     const int hidden = x.size(1);
     TORCH_CHECK(hidden % 8 == 0, "rmsnorm: hidden size ", hidden, " must be a multiple of 8");
-    TORCH_CHECK(groups >= 1 && hidden % groups == 0 && (hidden / groups) % 8 == 0, "rmsnorm: ", groups,
-                " groups must cut the hidden size ", hidden, " into equal parts of a multiple of 8 values");
+    TORCH_CHECK(groups >= 1 && hidden % groups == 0, "rmsnorm: ", groups, " groups must cut the hidden size ", hidden, " into equal parts");
+    TORCH_CHECK((hidden / groups) % 8 == 0 || (!center && !post_weight.has_value()), "rmsnorm: groups of a size that is no multiple of 8 "
+                "take no delta that is normed first");
     TORCH_CHECK(!center || (groups == 1 && x_scale == 1.0 && !write_normed), "layernorm: no groups, scale of the stream or normed stream");
     TORCH_CHECK(out_opt.has_value() || (write_normed && delta.has_value() && delta->dim() == 2),
                 "rmsnorm: without out the stream takes the normed row, and a delta tensor gives the dtype");

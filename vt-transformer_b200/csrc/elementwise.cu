@@ -224,6 +224,41 @@ __global__ void rmsnorm_kernel(float* __restrict__ x, const T* __restrict__ delt
     }
 }
 
+// Groups of a size that is no multiple of 8 (their rows do not start on 16-byte boundaries): a warp a (row, group), value by
+// value; the sum of squares in the order lane by lane, then over the lanes.  No delta that is normed first, no mean.
+template <typename T>
+__global__ void rmsnorm_narrow_groups_kernel(float* __restrict__ x, const T* __restrict__ delta, const float* __restrict__ parts,
+                                             int n_parts, const float* __restrict__ weight, float eps, T* __restrict__ out,
+                                             const int* __restrict__ rows, int n_tokens, int part, int* status, int row_size,
+                                             float x_scale, int write_normed) {
+    pdl_launch();
+    const int r = blockIdx.x;
+    const int t = rows ? rows[r] : r;
+    const int part0 = blockIdx.y * part;
+    pdl_wait();
+    if (t < 0 || t >= n_tokens) {
+        if (threadIdx.x == 0) set_status(status, kStatusBadRow, t);
+        return;
+    }
+    float* xr = x + (size_t)t * row_size + part0;
+    const size_t stride = (size_t)n_tokens * row_size;
+    float ss = 0.f;
+    for (int i = threadIdx.x; i < part; i += 32) {
+        float v = xr[i] * x_scale;
+        if (delta) v += to_float(delta[(size_t)t * row_size + part0 + i]);
+        for (int q = 0; parts && q < n_parts; ++q) v += parts[(size_t)t * row_size + part0 + i + q * stride];
+        xr[i] = v;
+        ss = fmaf(v, v, ss);
+    }
+    ss = warp_sum(ss);
+    const float rs = rsqrtf(ss / (float)part + eps);
+    for (int i = threadIdx.x; i < part; i += 32) {
+        const float y = weight[part0 + i] * xr[i] * rs;      // this lane's own write above
+        if (out) out[(size_t)r * row_size + part0 + i] = from_float<T>(y);
+        if (write_normed) xr[i] = y;
+    }
+}
+
 template <bool Center>
 static cudaError_t launch_norm(int out_dtype, float* x, const void* delta, const float* parts, int n_parts,
                                const float* weight, float eps, void* out, const int* rows, int n_rows, int n_tokens,
@@ -231,8 +266,17 @@ static cudaError_t launch_norm(int out_dtype, float* x, const void* delta, const
                                cudaStream_t stream, int groups = 1, float x_scale = 1.f, int write_normed = 0) {
     if (delta != nullptr && parts != nullptr) return cudaErrorInvalidValue;
     if (n_rows == 0) return cudaSuccess;
-    if (groups < 1 || hidden % groups || (hidden / groups) % 8 || (out == nullptr && !write_normed)) return cudaErrorInvalidValue;
+    if (groups < 1 || hidden % groups || (out == nullptr && !write_normed)) return cudaErrorInvalidValue;
     const int part = hidden / groups;                     // values that are normed together
+    if (part % 8) {
+        if (Center || post_weight != nullptr) return cudaErrorInvalidValue;
+        const dim3 grid_narrow(n_rows, groups);
+        if (out_dtype == kBF16)
+            return launch(rmsnorm_narrow_groups_kernel<__nv_bfloat16>, grid_narrow, 32, 0, stream, x, (const __nv_bfloat16*)delta, parts, n_parts,
+                          weight, eps, (__nv_bfloat16*)out, rows, n_tokens, part, status, hidden, x_scale, write_normed);
+        return launch(rmsnorm_narrow_groups_kernel<float>, grid_narrow, 32, 0, stream, x, (const float*)delta, parts, n_parts, weight, eps,
+                      (float*)out, rows, n_tokens, part, status, hidden, x_scale, write_normed);
+    }
     int threads = min(512, max(32, ((part / 8 + 31) / 32) * 32));
     const dim3 grid(n_rows, groups);
     if (out_dtype == kBF16)
