@@ -40,6 +40,9 @@ def test_configuration_reads_every_size_and_round_trips():
     assert cfg.layers[5].mlp.shared_ff is None
     assert [cfg.owner(i) for i in range(6)] == [0, 1, 2, 1, 0, 5]
     assert config_from_dict(cfg.to_dict()) == cfg
+    one = copy.deepcopy(cases.CONFIGS["lightning_alone"])
+    one["layers"][0]["mixer"]["decay"] = 0.9                       # one number stands for every head
+    assert config_from_dict(one).layers[0].mixer.decay == (0.9, 0.9, 0.9)
     for spoil, match in ((lambda c: c["layers"][0].__setitem__("type", "other"), "layers\\[0\\].*'other'"),
                          (lambda c: c["layers"][1]["mixer"].pop("kv_rank"), "layers\\[1\\].mixer.*'kv_rank'"),
                          (lambda c: c["layers"][1]["mixer"]["rot"].__setitem__("dims", 18), "rot.dims"),

@@ -198,6 +198,8 @@ def _layer(entry, where: str) -> GeponexLayer:
                                        second=kind == "latent_attention_2")
     elif kind == "lightning":
         decay = m.raw("decay")
+        if isinstance(decay, (int, float)) and not isinstance(decay, bool):      # one number for all heads
+            decay = [decay] * m.integer("heads", minimum=1)
         if not isinstance(decay, list) or not all(isinstance(d, (int, float)) and not isinstance(d, bool) for d in decay):
             raise ConfigError(f"{mw}: key 'decay' must be a list of numbers, one for each head")
         dim = m.integer("dim", minimum=1)
