@@ -47,9 +47,11 @@ namespace {
 
 constexpr int LAT_ROWS = 64;
 
-// DVT: the columns of O that the kernel has registers for (DV <= DVT); KBL: keys in a block.
-template <int DVT, int KBL>
-__global__ void __launch_bounds__(256, 1)
+// DVT: the columns of O that the kernel has registers for (DV <= DVT); KBL: keys in a block; MINB: CTAs an SM that the
+// registers are to leave room for (values of up to 256 numbers fit two CTAs of 128 registers a thread: four warps a
+// scheduler instead of two hide more of the fragment loads' and the products' latency).
+template <int DVT, int KBL, int MINB>
+__global__ void __launch_bounds__(256, MINB)
 attention_latent_kernel(const LatentParams p) {
     constexpr int THREADS = 256;
     constexpr int NJ = KBL / 8;               // tiles of 8 keys of a block
@@ -333,13 +335,13 @@ attention_latent_merge_kernel(const float* __restrict__ part, int n_splits, int 
     }
 }
 
-template <int DVT, int KBL>
+template <int DVT, int KBL, int MINB = 1>
 cudaError_t launch_latent_as(const LatentParams& p, int n_tiles, int head_groups, cudaStream_t stream) {
     static std::atomic<unsigned long long> done{0};
     const int bytes = (LAT_ROWS + 2 * KBL) * (p.D + 8) * 2 + 8 * (KBL / 8) * 32 * 16;
-    cudaError_t e = allow_dynamic_smem(attention_latent_kernel<DVT, KBL>, 200 * 1024, done);
+    cudaError_t e = allow_dynamic_smem(attention_latent_kernel<DVT, KBL, MINB>, 200 * 1024, done);
     if (e != cudaSuccess) return e;
-    e = launch(attention_latent_kernel<DVT, KBL>, dim3(n_tiles, head_groups, p.n_splits), dim3(256), bytes, stream, p);
+    e = launch(attention_latent_kernel<DVT, KBL, MINB>, dim3(n_tiles, head_groups, p.n_splits), dim3(256), bytes, stream, p);
     if (e != cudaSuccess || p.n_splits <= 1) return e;
     return launch(attention_latent_merge_kernel, dim3(n_tiles, p.heads), dim3(128), 0, stream, (const float*)p.part, p.n_splits, p.n_tokens,
                   p.heads, p.DV, p.cu_q, p.out, p.out_stride, p.out_col);
@@ -353,7 +355,7 @@ int attention_latent_tile_rows() { return LAT_ROWS; }
 // tile's queries with two blocks of keys within the shared memory
 bool attention_latent_supports(int key, int v_dim) {
     if (key % 16 || v_dim % 16 || v_dim < 16 || v_dim > 512 || v_dim > key) return false;
-    const int kbl = v_dim > 256 ? 32 : 64;
+    const int kbl = 32;
     return (LAT_ROWS + 2 * kbl) * (key + 8) * 2 + 8 * (kbl / 8) * 32 * 16 <= 200 * 1024;
 }
 
@@ -369,9 +371,9 @@ cudaError_t launch_attention_latent(const void* q, int q_stride, int q_col, void
                       cu_q, q_start, block_table, table_stride, reinterpret_cast<const int2*>(tiles), n_pages, heads, page_size, key,
                       v_dim, scale * 1.4426950408889634f, sinks, LAT_ROWS / hpt, hpt, n_splits, n_tokens, part};
     const int groups = (heads + hpt - 1) / hpt;
-    if (v_dim <= 64) return launch_latent_as<64, 64>(p, n_tiles, groups, stream);
-    if (v_dim <= 128) return launch_latent_as<128, 64>(p, n_tiles, groups, stream);
-    if (v_dim <= 256) return launch_latent_as<256, 64>(p, n_tiles, groups, stream);
+    if (v_dim <= 64) return launch_latent_as<64, 32, 2>(p, n_tiles, groups, stream);
+    if (v_dim <= 128) return launch_latent_as<128, 32, 2>(p, n_tiles, groups, stream);
+    if (v_dim <= 256) return launch_latent_as<256, 32, 2>(p, n_tiles, groups, stream);
     return launch_latent_as<512, 32>(p, n_tiles, groups, stream);
 }
 
