@@ -9,9 +9,9 @@
 // A tile is 64 rows of (token, head): a block of keys is brought into shared memory once for all of them (two-stage
 // cp.async pipeline), and serves as K in S = Q K^T and, its first DV columns read transposed, as V in O += P V (mma.sync
 // m16n8k16, P rounded to bfloat16).  The queries of the tile stay in shared memory (a row of D numbers does not fit the
-// registers).  Eight warps: a slab of 16 rows has two warps; each forms the slab's scores over one half of the D inner
-// numbers, the two add each other's half through shared memory (so both hold the same scores, maxima and sums), and each
-// owns one half of the columns of O.  The sink is where the running maximum and sum start: m = sink, l = 1.
+// registers).  A slab of 16 rows has two warps (or four); each forms the slab's scores over its share of the D inner
+// numbers, they add each other's shares through shared memory in a fixed order (so all hold the same scores, maxima and
+// sums), and each owns its share of the columns of O.  The sink is where the running maximum and sum start: m = sink, l = 1.
 // Prompt portions and single tokens run the same kernel (a single token's tile holds its heads).
 #include "attention_mma.cuh"
 #include "common.cuh"
@@ -50,13 +50,14 @@ constexpr int LAT_ROWS = 64;
 // DVT: the columns of O that the kernel has registers for (DV <= DVT); KBL: keys in a block; MINB: CTAs an SM that the
 // registers are to leave room for (values of up to 256 numbers fit two CTAs of 128 registers a thread: four warps a
 // scheduler instead of two hide more of the fragment loads' and the products' latency).
-template <int DVT, int KBL, int MINB>
-__global__ void __launch_bounds__(256, MINB)
+template <int DVT, int KBL, int MINB, int WPS>
+__global__ void __launch_bounds__(128 * WPS, MINB)
 attention_latent_kernel(const LatentParams p) {
-    constexpr int THREADS = 256;
+    constexpr int WARPS = 4 * WPS;            // four slabs of 16 rows, WPS warps a slab
+    constexpr int THREADS = 32 * WARPS;
     constexpr int NJ = KBL / 8;               // tiles of 8 keys of a block
     constexpr int NK = KBL / 16;              // steps of 16 keys in the product with the values
-    constexpr int HALF = DVT / 2;             // columns of O that a warp owns
+    constexpr int HALF = DVT / WPS;           // columns of O that a warp owns
     constexpr int ND = HALF / 16;             // steps of 16 of them
     const int D = p.D, DV = p.DV, LD = D + 8; // padded rows: conflict-free fragment loads, 16-byte aligned
     extern __shared__ __align__(16) unsigned char smem_raw[];
@@ -67,10 +68,10 @@ attention_latent_kernel(const LatentParams p) {
     pdl_launch();
     pdl_wait();
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31, gq = lane >> 2, tq = lane & 3;
-    const int rg = warp >> 1, side = warp & 1, col0 = side * HALF;
+    const int rg = warp / WPS, side = warp % WPS, col0 = side * HALF;
     // the pair's warps form the slab's scores over one half of the D inner numbers each and add the other's half
-    const int ks_split = (D / 16 + 1) / 2;
-    const int ks_lo = side ? ks_split : 0, ks_hi = side ? D / 16 : ks_split;
+    const int ks_per = (D / 16 + WPS - 1) / WPS;
+    const int ks_lo = min(D / 16, side * ks_per), ks_hi = min(D / 16, ks_lo + ks_per);
     const int head0 = blockIdx.y * p.heads_per_tile;
     const int nheads = min(p.heads_per_tile, p.heads - head0);
     int seq = blockIdx.x, tok0 = 0;
@@ -119,7 +120,7 @@ attention_latent_kernel(const LatentParams p) {
 
     const int KC = D / 8;                              // 16-byte pieces in a row
     // the tile's queries: a warp a row at a time
-    for (int r = warp; r < LAT_ROWS; r += 8) {
+    for (int r = warp; r < LAT_ROWS; r += WARPS) {
         const int tk = r / p.heads_per_tile, hh = r % p.heads_per_tile;
         const bool ok = tk < ntok && hh < nheads;
         const __nv_bfloat16* src = p.q + (size_t)(q_begin + tok0 + (ok ? tk : 0)) * p.q_stride + p.q_col + (size_t)(head0 + (ok ? hh : 0)) * D;
@@ -128,7 +129,7 @@ attention_latent_kernel(const LatentParams p) {
     const int* table = p.block_table + (size_t)seq * p.table_stride;
     auto load_block = [&](int blk, int stage) {
         const int kb = blk * KBL;
-        for (int r = warp; r < KBL; r += 8) {
+        for (int r = warp; r < KBL; r += WARPS) {
             const int key = kb + r;
             bool ok = key < key_hi;
             size_t base = 0;
@@ -197,12 +198,26 @@ attention_latent_kernel(const LatentParams p) {
             float4* mine = xch + (size_t)warp * NJ * 32 + lane;
 #pragma unroll
             for (int j = 0; j < NJ; ++j) mine[j * 32] = make_float4(s[j][0], s[j][1], s[j][2], s[j][3]);
-            asm volatile("bar.sync %0, 64;\n" ::"r"(1 + rg) : "memory");          // the two warps of the slab
-            const float4* theirs = xch + (size_t)(warp ^ 1) * NJ * 32 + lane;
+            asm volatile("bar.sync %0, %1;\n" ::"r"(1 + rg), "n"(32 * WPS) : "memory");   // the warps of the slab
+            if (WPS == 2) {
+                const float4* theirs = xch + (size_t)(warp ^ 1) * NJ * 32 + lane;
 #pragma unroll
-            for (int j = 0; j < NJ; ++j) {                                        // a + b = b + a: both warps hold the same sums
-                const float4 t = theirs[j * 32];
-                s[j][0] += t.x; s[j][1] += t.y; s[j][2] += t.z; s[j][3] += t.w;
+                for (int j = 0; j < NJ; ++j) {                                    // a + b = b + a: both warps hold the same sums
+                    const float4 t = theirs[j * 32];
+                    s[j][0] += t.x; s[j][1] += t.y; s[j][2] += t.z; s[j][3] += t.w;
+                }
+            } else {
+                // all parts in the order of the warps, the own one from shared memory too: every warp holds the same sums
+#pragma unroll
+                for (int j = 0; j < NJ; ++j) {
+                    float4 a = xch[((size_t)(rg * WPS) * NJ + j) * 32 + lane];
+#pragma unroll
+                    for (int w = 1; w < WPS; ++w) {
+                        const float4 t = xch[((size_t)(rg * WPS + w) * NJ + j) * 32 + lane];
+                        a.x += t.x; a.y += t.y; a.z += t.z; a.w += t.w;
+                    }
+                    s[j][0] = a.x; s[j][1] = a.y; s[j][2] = a.z; s[j][3] = a.w;
+                }
             }
         }
         // mask, running maximum and sum (log2 domain)
@@ -335,13 +350,13 @@ attention_latent_merge_kernel(const float* __restrict__ part, int n_splits, int 
     }
 }
 
-template <int DVT, int KBL, int MINB = 1>
+template <int DVT, int KBL, int MINB = 1, int WPS = 2>
 cudaError_t launch_latent_as(const LatentParams& p, int n_tiles, int head_groups, cudaStream_t stream) {
     static std::atomic<unsigned long long> done{0};
-    const int bytes = (LAT_ROWS + 2 * KBL) * (p.D + 8) * 2 + 8 * (KBL / 8) * 32 * 16;
-    cudaError_t e = allow_dynamic_smem(attention_latent_kernel<DVT, KBL, MINB>, 200 * 1024, done);
+    const int bytes = (LAT_ROWS + 2 * KBL) * (p.D + 8) * 2 + 4 * WPS * (KBL / 8) * 32 * 16;
+    cudaError_t e = allow_dynamic_smem(attention_latent_kernel<DVT, KBL, MINB, WPS>, 200 * 1024, done);
     if (e != cudaSuccess) return e;
-    e = launch(attention_latent_kernel<DVT, KBL, MINB>, dim3(n_tiles, head_groups, p.n_splits), dim3(256), bytes, stream, p);
+    e = launch(attention_latent_kernel<DVT, KBL, MINB, WPS>, dim3(n_tiles, head_groups, p.n_splits), dim3(128 * WPS), bytes, stream, p);
     if (e != cudaSuccess || p.n_splits <= 1) return e;
     return launch(attention_latent_merge_kernel, dim3(n_tiles, p.heads), dim3(128), 0, stream, (const float*)p.part, p.n_splits, p.n_tokens,
                   p.heads, p.DV, p.cu_q, p.out, p.out_stride, p.out_col);
@@ -356,7 +371,8 @@ int attention_latent_tile_rows() { return LAT_ROWS; }
 bool attention_latent_supports(int key, int v_dim) {
     if (key % 16 || v_dim % 16 || v_dim < 16 || v_dim > 512 || v_dim > key) return false;
     const int kbl = 32;
-    return (LAT_ROWS + 2 * kbl) * (key + 8) * 2 + 8 * (kbl / 8) * 32 * 16 <= 200 * 1024;
+    const int warps = v_dim > 256 ? 16 : 8;
+    return (LAT_ROWS + 2 * kbl) * (key + 8) * 2 + warps * (kbl / 8) * 32 * 16 <= 200 * 1024;
 }
 
 cudaError_t launch_attention_latent(const void* q, int q_stride, int q_col, void* out, int out_stride, int out_col, const void* pages,
@@ -374,7 +390,10 @@ cudaError_t launch_attention_latent(const void* q, int q_stride, int q_col, void
     if (v_dim <= 64) return launch_latent_as<64, 32, 2>(p, n_tiles, groups, stream);
     if (v_dim <= 128) return launch_latent_as<128, 32, 2>(p, n_tiles, groups, stream);
     if (v_dim <= 256) return launch_latent_as<256, 32, 2>(p, n_tiles, groups, stream);
-    return launch_latent_as<512, 32>(p, n_tiles, groups, stream);
+    // wider values: one CTA an SM.  A step of single tokens runs four warps a slab (measured at rows of 576 numbers and 32
+    // heads: 70 us against 79 us for 64 sequences of 1,024 keys); prompt portions two (3.50 ms against 3.61 ms for 4,096 tokens)
+    if (p.tiles == nullptr) return launch_latent_as<512, 32, 1, 4>(p, n_tiles, groups, stream);
+    return launch_latent_as<512, 32, 1, 2>(p, n_tiles, groups, stream);
 }
 
 }  // namespace vtb
