@@ -369,8 +369,8 @@ def attention_differential(y, q_col: int, out, out_col: int, out_scale: float, k
                                          sub_eps=sub_eps)
 
 
-LATENT_TARGET_CTAS = 296     # CTAs that a step of single tokens aims at (two for each SM), and the most runs a sequence is cut into
-LATENT_MAX_RUNS = 16
+LATENT_TARGET_CTAS = 296     # CTAs that the latent attention of a step of single tokens aims at (two for each SM)
+LATENT_MAX_RUNS = 16         # the most runs of keys that a sequence is cut into for that (the merge kernel's limit)
 
 
 def attention_latent(q, q_col: int, out, out_col: int, pages, ctx, block_table, heads: int, key: int, v_dim: int, scale: float,
@@ -380,7 +380,8 @@ def attention_latent(q, q_col: int, out, out_col: int, pages, ctx, block_table, 
     ``v_dim`` numbers every head's value; out[t, out_col + h * v_dim + :] = sum_j p_j row_j[:v_dim] with
     p = softmax_j(scale q . row_j) over the keys j up to the token's position.  ``sinks`` [heads] float32: exp(sinks[h])
     joins the denominator (no key, no value, not scaled).  bfloat16 at the sizes the tensor-core kernel takes runs that
-    kernel (tiles of 64 rows of (token, head) that share each block of keys; a single token's tile holds its heads);
+    kernel (tiles of 64 rows of (token, head) that share each block of keys; a single token's tile holds its heads, and in a
+    step of single tokens every sequence's keys are cut into runs with a CTA each, merged in the order of the runs);
     everything else, and all of float32, the plain kernel."""
     be = backend()
     if (q.dtype == torch.bfloat16 and ATTENTION_KERNEL in ("auto", "mma") and q_col % 8 == 0 and out_col % 2 == 0
