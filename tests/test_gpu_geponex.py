@@ -30,12 +30,6 @@ def _logits(folder, tokens):
     return helpers.plain_logits(folder, tokens)
 
 
-def _sensitivity(folder, base, ask, where, tok):
-    ids = list(base)
-    ids[where] = tok
-    return float((_logits(folder, ids)[ask] - _logits(folder, base)[ask]).abs().max())
-
-
 # ----------------------------------------------------------------------------- kernels against the plain functions
 
 
