@@ -82,13 +82,14 @@ def test_norm_kernel_in_groups_after_the_scaled_sum(dtype, width, groups):
 def test_activation_kernels(dtype):
     from vt_transformer_b200 import ops
     g = torch.Generator().manual_seed(11)
-    z = (torch.randn((9, 40), generator=g) * 3).to(dtype)
     p, q = torch.tensor(0.3, dtype=F), torch.tensor(-0.4, dtype=F)
     sp = torch.nn.functional.softplus
-    out = torch.empty_like(z, device=DEV)
-    ops.xielu(z.to(DEV), out, float(sp(p)), float(0.5 + sp(q)))
-    ref = plain.xielu(z.double(), p, q)
-    assert float(((out.double().cpu() - ref).abs() / (1 + ref.abs())).max()) <= (1e-6 if dtype == torch.float32 else 8e-3)
+    for shape in ((9, 40), (9, 41), (300, 1024)):            # eight values a thread, and one where the count is no multiple of 8
+        z = (torch.randn(shape, generator=g) * 3).to(dtype)
+        out = torch.empty_like(z, device=DEV)
+        ops.xielu(z.to(DEV), out, float(sp(p)), float(0.5 + sp(q)))
+        ref = plain.xielu(z.double(), p, q)
+        assert float(((out.double().cpu() - ref).abs() / (1 + ref.abs())).max()) <= (1e-6 if dtype == torch.float32 else 8e-3)
     # gate and up side by side and in alternating runs of 8, with a second clamp from a column on
     n, split = 48, 32
     gate, up = (torch.randn((9, n), generator=g) * 2).to(dtype), (torch.randn((9, n), generator=g) * 2).to(dtype)
