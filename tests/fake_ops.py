@@ -232,13 +232,18 @@ def delta_scan(y, r_col, k_col, v_col, a_col, w1_col, w2, w0, a_bias, decay_rate
 
 
 def attention_prepare(y, q_col, k_col, v_col, positions, token_seq, frequencies, norm_eps, k_cache, v_cache, block_table,
-                      heads, kv_heads, dim, v_dim, store, status=None, v_heads=None, q_weight=None, k_weight=None, norm_first=False):
+                      heads, kv_heads, dim, v_dim, store, status=None, v_heads=None, q_weight=None, k_weight=None, norm_first=False,
+                      whole_projection=False, rot_mult=1.0, q_temp_coef=0.0, q_temp_every=1):
     T = y.shape[0]
     page_size = k_cache.shape[2]
     live = token_seq >= 0
     v_heads = kv_heads if v_heads is None else v_heads
 
     def normed(x, w):
+        if norm_eps >= 0 and whole_projection:       # one mean square over all heads, a weight for every channel
+            flat = x.reshape(x.shape[0], -1)
+            flat = flat * torch.rsqrt((flat * flat).mean(dim=-1, keepdim=True) + norm_eps)
+            return (flat * w if w is not None else flat).reshape(x.shape)
         if norm_eps >= 0:
             x = x * torch.rsqrt((x * x).mean(dim=-1, keepdim=True) + norm_eps)
             if w is not None:
@@ -251,7 +256,7 @@ def attention_prepare(y, q_col, k_col, v_col, positions, token_seq, frequencies,
         if frequencies is not None and frequencies.numel():
             half = frequencies.numel()
             ang = positions.float()[:, None] * frequencies.float()[None, :]
-            c, s = torch.cos(ang)[:, None, :], torch.sin(ang)[:, None, :]
+            c, s = torch.cos(ang)[:, None, :] * rot_mult, torch.sin(ang)[:, None, :] * rot_mult
             a, b = x[..., :half].clone(), x[..., half:2 * half].clone()
             x[..., :half] = a * c - b * s
             x[..., half:2 * half] = b * c + a * s
@@ -260,6 +265,9 @@ def attention_prepare(y, q_col, k_col, v_col, positions, token_seq, frequencies,
         return x
 
     q = turn(y[:, q_col:q_col + heads * dim].float().view(T, heads, dim).clone(), q_weight)
+    if q_temp_coef != 0.0:
+        steps = torch.div(positions.clamp(min=0) + 1, q_temp_every, rounding_mode="floor").float()
+        q = q * (1.0 + q_temp_coef * torch.log(steps + 1.0))[:, None, None]
     y[:, q_col:q_col + heads * dim] = q.reshape(T, heads * dim).to(y.dtype)
     if not store:
         return
@@ -277,7 +285,7 @@ def attention_prepare(y, q_col, k_col, v_col, positions, token_seq, frequencies,
 
 def attention_general(y, q_col, out, out_col, out_scale, k_cache, v_cache, positions, token_seq, block_table, heads, kv_heads,
                       dim, v_dim, window, chunk, scale, status=None, keep_first=0, maps=1, lam=0.0, sub_eps=0.0, sinks=None,
-                      values_in_keys=False):
+                      values_in_keys=False, softcap=0.0, gate_mode=0, gate_col=0):
     T = y.shape[0]
     page_size = k_cache.shape[2]
     g = heads // kv_heads
@@ -299,11 +307,17 @@ def attention_general(y, q_col, out, out_col, out_scale, k_cache, v_cache, posit
         for h in range(heads):
             if maps == 1:
                 sc = (keys[:, h // g, :] @ q[t, h]) * scale
+                if softcap > 0:
+                    sc = softcap * torch.tanh(sc / softcap)
                 if sinks is not None:            # one more term in the denominator, without a value
                     pr = torch.softmax(torch.cat([sc, sinks[h:h + 1].float()]), dim=0)[:-1]
                 else:
                     pr = torch.softmax(sc, dim=0)
                 o = out_scale * (pr @ vals[:, h // g, :])
+                if gate_mode == 1:
+                    o = o * torch.sigmoid(y[t, gate_col + h].float())
+                elif gate_mode == 2:
+                    o = o * torch.sigmoid(y[t, gate_col + h * v_dim:gate_col + (h + 1) * v_dim].float())
             else:
                 a = [torch.softmax((keys[:, (h // g) * 2 + m, :] @ q[t, 2 * h + m]) * scale, dim=0) @ vals[:, h // g, :] for m in range(2)]
                 o = a[0] - lam * a[1]
@@ -515,3 +529,87 @@ def gate_clamp(gu, out, interleave, alpha, limit, split, limit2):
     g = torch.minimum(g, lim)
     u = torch.maximum(torch.minimum(u, lim), -lim)
     out.copy_((g * torch.sigmoid(alpha * g) * (u + 1.0)).to(out.dtype))
+
+
+# ---- the kernels of the delta rule with one decay a head, the matrix memory, and mixers whose results are normed and added ----
+
+
+def _conv_inputs(y, col, width, tail, tail_at, row, a, b):
+    """The inputs of a convolution for the step's tokens [a, b) of a request, with the kept inputs in front of them."""
+    x = y[a:b, col:col + width].float()
+    if tail is None:
+        return x
+    return torch.cat([tail[row][:, tail_at:tail_at + width], x], dim=0)
+
+
+def gated_delta_scan(y, q_col, k_col, v_col, b_col, a_col, conv_q, conv_k, conv_v, a_log, dt_bias, key_eps, q_scale, state, tail,
+                     cu_q, rows, o, heads, kv_heads, dim, v_dim, status=None, most_threads=0):
+    yf = y.float()
+    nq, nv = kv_heads * dim, heads * v_dim
+    group = heads // kv_heads
+    for row, a, b in _sequences(cu_q, rows):
+        n = b - a
+        made = []
+        for col, width, w, at in ((q_col, nq, conv_q, 0), (k_col, nq, conv_k, nq), (v_col, nv, conv_v, 2 * nq)):
+            x = _conv_inputs(yf, col, width, tail, at, row, a, b)
+            if w is None:
+                z = x[-n:]
+            else:
+                taps = w.shape[1]
+                if x.shape[0] < n + taps - 1:
+                    x = torch.cat([torch.zeros((n + taps - 1 - x.shape[0], width)), x], dim=0)
+                z = sum(x[j:j + n] * w[:, j][None, :] for j in range(taps))
+            made.append(z * torch.sigmoid(z))
+        q, k, v = made[0].view(n, kv_heads, dim), made[1].view(n, kv_heads, dim), made[2].view(n, heads, v_dim)
+        q = q * torch.rsqrt((q * q).sum(dim=-1, keepdim=True) + key_eps) * q_scale
+        k = k * torch.rsqrt((k * k).sum(dim=-1, keepdim=True) + key_eps)
+        beta = torch.sigmoid(yf[a:b, b_col:b_col + heads])
+        decay = torch.exp(-torch.exp(a_log) * torch.nn.functional.softplus(yf[a:b, a_col:a_col + heads] + dt_bias))
+        S = state[row].clone()
+        for t in range(n):
+            kk, qq = k[t].repeat_interleave(group, dim=0), q[t].repeat_interleave(group, dim=0)
+            S = decay[t][:, None, None] * S
+            u = beta[t][:, None] * (v[t] - torch.einsum("hdv,hd->hv", S, kk))
+            S = S + kk[:, :, None] * u[:, None, :]
+            o[a + t] = torch.einsum("hdv,hd->hv", S, qq).reshape(-1)
+        state[row] = S
+
+
+def conv_tail_update(y, cols, widths, tail, cu_q, rows, status=None):
+    keep = tail.shape[1]
+    for row, a, b in _sequences(cu_q, rows):
+        x = torch.cat([y[a:b, c:c + w].float() for c, w in zip(cols, widths)], dim=1)
+        tail[row] = torch.cat([tail[row], x], dim=0)[-keep:]
+
+
+def memory_scan(y, q_col, k_col, v_col, i_col, f_col, i_bias, f_bias, gate_cap, q_scale, den_eps, state, cu_q, rows, o, heads, dim,
+                v_dim, status=None, most_threads=0):
+    yf = y.float()
+    T = y.shape[0]
+    q = yf[:, q_col:q_col + heads * dim].view(T, heads, dim) * q_scale
+    k = yf[:, k_col:k_col + heads * dim].view(T, heads, dim)
+    v = yf[:, v_col:v_col + heads * v_dim].view(T, heads, v_dim)
+    ig = gate_cap * torch.tanh((yf[:, i_col:i_col + heads] + i_bias) / gate_cap)
+    fg = torch.nn.functional.logsigmoid(gate_cap * torch.tanh((yf[:, f_col:f_col + heads] + f_bias) / gate_cap))
+    for row, a, b in _sequences(cu_q, rows):
+        S, n, m = state[row, :, :dim, :v_dim].clone(), state[row, :, :dim, v_dim].clone(), state[row, :, dim, 0].clone()
+        for t in range(a, b):
+            m_new = torch.maximum(fg[t] + m, ig[t])
+            keep, take = torch.exp(fg[t] + m - m_new), torch.exp(ig[t] - m_new)
+            S = keep[:, None, None] * S + take[:, None, None] * k[t][:, :, None] * v[t][:, None, :]
+            n = keep[:, None] * n + take[:, None] * k[t]
+            m = m_new
+            den = torch.maximum((n * q[t]).sum(dim=-1).abs(), torch.exp(-m)) + den_eps
+            o[t] = (torch.einsum("hdv,hd->hv", S, q[t]) / den[:, None]).reshape(-1)
+        state[row, :, :dim, :v_dim], state[row, :, :dim, v_dim], state[row, :, dim, 0] = S, n, m
+
+
+def normed_sum(parts, weights, eps, scales, out):
+    total = torch.zeros_like(out)
+    for p, w, c in zip(parts, weights, scales):
+        total = total + c * w * p * torch.rsqrt((p * p).mean(dim=-1, keepdim=True) + eps)
+    out.copy_(total)
+
+
+def add_rows(x, other):
+    x.add_(other)

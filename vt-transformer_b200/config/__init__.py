@@ -1,4 +1,5 @@
 from .base import ConfigError, KeyReader, ModelConfig
+from .fosepel import FosepelConfig
 from .geponex import GeponexConfig
 from .qwen2 import Qwen2Config
 from .sisetar import SisetarConfig

@@ -1,3 +1,3 @@
 """Models.  Importing the package registers the built-in architectures."""
-from . import geponex, qwen2, sisetar, vegilix  # noqa: F401
+from . import fosepel, geponex, qwen2, sisetar, vegilix  # noqa: F401
 from .base import DecoderModel

@@ -111,7 +111,11 @@ class DecoderModel:
         """Runs the step's tokens and returns float32 logits [wanted rows, vocab].
         ``views[slot]`` is the cache view of a slot for this step."""
         stream = ResidualStream(self.embedding.forward(ctx), status=ctx.status)
+        # a run that adds the embedding's output once more reads a second copy of it (the stream itself moves on)
+        first = self.embedding.forward(ctx) if any(run.add_embedding for run in self.spec.order) else None
         for run in self.spec.order:
+            if run.add_embedding:
+                self.rt.ops.add_rows(stream.x, first)
             view = None
             if isinstance(run.cache, (tuple, list)):
                 view = tuple(self._view(views, slot, run.writes) for slot in run.cache)

@@ -278,23 +278,32 @@ def retention_scan(y, q_col: int, k_col: int, v_col: int, decay: torch.Tensor, k
 
 def attention_prepare(y, q_col: int, k_col: int, v_col: int, ctx, frequencies, norm_eps, k_cache, v_cache, block_table,
                       heads: int, kv_heads: int, dim: int, v_dim: int, store: bool = True, status=None, v_heads=None,
-                      q_weight=None, k_weight=None, norm_first: bool = False) -> None:
+                      q_weight=None, k_weight=None, norm_first: bool = False, whole_projection: bool = False,
+                      rot_mult: float = 1.0, q_temp=None) -> None:
     """What the general attention does to a step's q, k and v (columns of ``y``) before its keys are walked: the
     first 2 * len(frequencies) dimensions of every head of q and k are rotated, pairs (i, i + len), by
     position * frequencies[i] (a 32-bit product; ``frequencies`` None: no rotation); with ``norm_eps`` not None,
     every head of q and k is divided by sqrt(mean(.^2) + norm_eps) and multiplied by ``q_weight`` / ``k_weight``
     ([dim] float32, or None), after the rotation or, with ``norm_first``, before it; q is written back into ``y``, k and
     v go into their pages ([pages, kv_heads, page_size, dim] and [pages, v_heads, page_size, v_dim]; ``v_heads``
-    None: as many as kv_heads) if ``store``."""
-    backend().attention_prepare(y, int(q_col), int(k_col), int(v_col), ctx.positions, ctx.token_seq, frequencies,
-                                -1.0 if norm_eps is None else float(norm_eps), k_cache, v_cache, block_table, int(heads),
-                                int(kv_heads), int(dim), int(v_dim), bool(store), status,
-                                int(kv_heads if v_heads is None else v_heads), q_weight, k_weight, bool(norm_first))
+    None: as many as kv_heads) if ``store``.  ``whole_projection`` (with ``norm_first``): the mean square is taken over all
+    heads of q together (and of k) and the weights are [heads * dim] and [kv_heads * dim].  ``rot_mult`` multiplies cos and
+    sin.  ``q_temp`` = (c, n): q is multiplied by 1 + c ln(floor((position + 1) / n) + 1), last of all."""
+    args = (y, int(q_col), int(k_col), int(v_col), ctx.positions, ctx.token_seq, frequencies,
+            -1.0 if norm_eps is None else float(norm_eps), k_cache, v_cache, block_table, int(heads),
+            int(kv_heads), int(dim), int(v_dim), bool(store), status,
+            int(kv_heads if v_heads is None else v_heads), q_weight, k_weight, bool(norm_first))
+    if whole_projection or rot_mult != 1.0 or q_temp is not None:
+        coef, every = (float(q_temp[0]), int(q_temp[1])) if q_temp is not None else (0.0, 1)
+        backend().attention_prepare(*args, bool(whole_projection), float(rot_mult), coef, every)
+    else:
+        backend().attention_prepare(*args)
 
 
 def attention_general(y, q_col: int, out, out_col: int, out_scale: float, k_cache, v_cache, ctx, block_table, heads: int,
                       kv_heads: int, dim: int, v_dim: int, window, chunk, scale: float, status=None, keep_first: int = 0,
-                      maps: int = 1, lam: float = 0.0, sub_eps: float = 0.0, sinks=None, values_in_keys: bool = False):
+                      maps: int = 1, lam: float = 0.0, sub_eps: float = 0.0, sinks=None, values_in_keys: bool = False,
+                      softcap=None, gate: str = "none", gate_col: int = 0):
     """out[t, out_col + h * v_dim + :] = out_scale * softmax(scale * q . k_j) v_j over the keys j that token t at
     position p sees: j <= p, and j > p - window or j < keep_first (if a window is given), and j // chunk == p // chunk
     (if chunks are).  q is read at column ``q_col`` of ``y``; keys of size ``dim`` and values of size ``v_dim`` from
@@ -302,12 +311,74 @@ def attention_general(y, q_col: int, out, out_col: int, out_scale: float, k_cach
     [pages, kv_heads * 2, page_size, dim]); with a_1 and a_2 the two attentions over the same values,
     o = a_1 - lam * a_2 and out = out_scale * o / sqrt(mean(o^2) + sub_eps), all in 32-bit.
     ``sinks`` [heads] float32: one more term exp(sinks[h]) in the softmax's denominator, without a key or a value and not
-    scaled.  ``values_in_keys``: a value is the first ``v_dim`` numbers of its key's row (``v_cache`` is ``k_cache``)."""
-    backend().attention_general(y, int(q_col), out, int(out_col), float(out_scale), k_cache, v_cache, ctx.positions,
-                                ctx.token_seq, block_table, int(heads), int(kv_heads), int(dim), int(v_dim),
-                                int(window) if window else 0, int(chunk) if chunk else 0, float(scale), status,
-                                int(keep_first), int(maps), float(lam), float(sub_eps), sinks, bool(values_in_keys))
+    scaled.  ``values_in_keys``: a value is the first ``v_dim`` numbers of its key's row (``v_cache`` is ``k_cache``).
+    ``softcap`` c: a score becomes c tanh(score / c) after the scale.  ``gate`` "head": head h's result is multiplied by
+    sigmoid(y[t, gate_col + h]); "element": element i of it by sigmoid(y[t, gate_col + h * v_dim + i])."""
+    args = (y, int(q_col), out, int(out_col), float(out_scale), k_cache, v_cache, ctx.positions,
+            ctx.token_seq, block_table, int(heads), int(kv_heads), int(dim), int(v_dim),
+            int(window) if window else 0, int(chunk) if chunk else 0, float(scale), status,
+            int(keep_first), int(maps), float(lam), float(sub_eps), sinks, bool(values_in_keys))
+    if softcap or gate != "none":
+        backend().attention_general(*args, float(softcap) if softcap else 0.0, _ATTENTION_GATES[gate], int(gate_col))
+    else:
+        backend().attention_general(*args)
     return out
+
+
+_ATTENTION_GATES = {"none": 0, "head": 1, "element": 2}
+
+
+def gated_delta_scan(y, q_col: int, k_col: int, v_col: int, b_col: int, a_col: int, conv_q, conv_k, conv_v, a_log: torch.Tensor,
+                     dt_bias: torch.Tensor, key_eps: float, q_scale: float, state: torch.Tensor, tail, ctx, o: torch.Tensor,
+                     heads: int, kv_heads: int, dim: int, v_dim: int, status=None):
+    """The delta rule with one decay a head over the step's tokens, sequence by sequence and head by head, in the order of
+    the tokens.  q and k ([kv_heads * dim]) and v ([heads * v_dim]) are columns of ``y``; each passes a causal convolution
+    over time, channel by channel (``conv_q``, ``conv_k``, ``conv_v``: float32 [channels, taps], the last tap the present
+    token's; None: no convolution), whose inputs before the step's first token come from ``tail`` [request rows, taps - 1,
+    channels of q + k + v] (float32, oldest first; this kernel reads it, ``conv_tail_update`` renews it), and silu; q and k
+    are divided, head by head, by sqrt(sum(.^2) + key_eps), q multiplied by ``q_scale``.  beta = sigmoid(y at ``b_col`` + h),
+    g = exp(-exp(a_log[h]) softplus(y at ``a_col`` + h + dt_bias[h])).  S <- g S; u = beta (v - S^T k); S <- S + k u^T;
+    o = S^T q, head h with q/k head h // (heads / kv_heads).  ``state`` [request rows, heads, dim, v_dim] float32 is read at
+    the step's ``ctx.rows`` and left as after the last token; ``o`` [T, heads * v_dim] float32.  All in 32-bit."""
+    backend().gated_delta_scan(y, int(q_col), int(k_col), int(v_col), int(b_col), int(a_col), conv_q, conv_k, conv_v, a_log, dt_bias,
+                               float(key_eps), float(q_scale), state, tail, ctx.cu_q, ctx.rows, o, int(heads), int(kv_heads),
+                               int(dim), int(v_dim), status, _scan_threads(ctx))
+    return o
+
+
+def conv_tail_update(y, cols, widths, tail: torch.Tensor, ctx, status=None) -> None:
+    """Renews what a short convolution keeps of a request: ``tail`` [request rows, n, channels] (float32) holds the last n
+    inputs of every channel, oldest first; the channels are the columns [cols[i], cols[i] + widths[i]) of ``y`` one group
+    after the other.  After the step it holds the last n inputs again: the step's last tokens, and before them what it held."""
+    backend().conv_tail_update(y, [int(c) for c in cols], [int(w) for w in widths], tail, ctx.cu_q, ctx.rows, status)
+
+
+def memory_scan(y, q_col: int, k_col: int, v_col: int, i_col: int, f_col: int, i_bias: torch.Tensor, f_bias: torch.Tensor,
+                gate_cap: float, q_scale: float, den_eps: float, state: torch.Tensor, ctx, o: torch.Tensor, heads: int, dim: int,
+                v_dim: int, status=None):
+    """A matrix of memory a head with exponential gates over the step's tokens, in their order.  q, k ([heads * dim]) and v
+    ([heads * v_dim]) are columns of ``y``; i = c tanh((y at ``i_col`` + h + i_bias[h]) / c) and
+    f = log sigmoid(c tanh((y at ``f_col`` + h + f_bias[h]) / c)), c = ``gate_cap``.  m' = max(f + m, i);
+    S <- exp(f + m - m') S + exp(i - m') k v^T; n likewise with k alone; o = S^T (q_scale q) / (max(|n . q_scale q|, exp(-m')) + den_eps).
+    ``state`` [request rows, heads, dim + 1, v_dim + 1] float32: S in [:dim, :v_dim], n in [:dim, v_dim], m at [dim, 0].
+    ``o`` [T, heads * v_dim] float32.  All in 32-bit."""
+    backend().memory_scan(y, int(q_col), int(k_col), int(v_col), int(i_col), int(f_col), i_bias, f_bias, float(gate_cap),
+                          float(q_scale), float(den_eps), state, ctx.cu_q, ctx.rows, o, int(heads), int(dim), int(v_dim), status,
+                          _scan_threads(ctx))
+    return o
+
+
+def normed_sum(parts, weights, eps: float, scales, out: torch.Tensor) -> torch.Tensor:
+    """out = sum_i scales[i] * weights[i] * parts[i] / sqrt(mean(parts[i]^2) + eps), row by row, for float32 parts [T, H]
+    (up to four) and weights [H]; all in 32-bit, the sum in the order of i."""
+    backend().normed_sum(list(parts), list(weights), float(eps), [float(c) for c in scales], out)
+    return out
+
+
+def add_rows(x: torch.Tensor, other: torch.Tensor) -> torch.Tensor:
+    """x += other for float32 [T, H] (the residual stream and another stream of its shape)."""
+    backend().add_rows(x, other)
+    return x
 
 
 # Picks (tokens of a step times the experts each uses) from which a mixture of experts groups its tokens by expert
@@ -897,6 +968,6 @@ def _counted(fn):
     return wrapper
 
 
-for _name in ("embedding", "logits_scale_cap", "rmsnorm", "layernorm", "polynorm", "scale_into", "head_norm_gate", "gla_scan", "delta_scan", "retention_scan", "route_experts", "attention_differential", "route_topk", "expert_lists", "gather_picks", "combine_picks",
+for _name in ("gated_delta_scan", "conv_tail_update", "memory_scan", "normed_sum", "add_rows", "embedding", "logits_scale_cap", "rmsnorm", "layernorm", "polynorm", "scale_into", "head_norm_gate", "gla_scan", "delta_scan", "retention_scan", "route_experts", "attention_differential", "route_topk", "expert_lists", "gather_picks", "combine_picks",
               "token_shift", "latent_prepare", "head_matmul", "attention_latent", "xielu", "gate_clamp", "attention_prepare", "attention_general", "silu_mul", "rope_store", "linear", "paged_attention", "argmax", "sample"):  # the others count where they launch
     globals()[_name] = _counted(globals()[_name])

@@ -4,6 +4,6 @@ from .base import (Block, CacheView, Embedding, FeedForward, Head, KVCacheSpec, 
                    ResidualStream, Runtime, StateLayout, StateSpec, PagedLayout, build_part, register_cache_kind, register_part,
                    unregister_cache_kind, unregister_part)
 from .specs import (AttentionSpec, BlockSpec, DeltaRuleSpec, DifferentialAttentionSpec, EmbeddingSpec, ExpertsSpec, FeedForwardSpec,
-                    GatedLinearAttentionSpec, GatedMLPSpec, LatentAttentionSpec, LightningSpec, RetentionSpec, XieluMLPSpec,
+                    GatedDeltaSpec, GatedLinearAttentionSpec, GatedMLPSpec, LatentAttentionSpec, MatrixMemorySpec, NormedParallelSpec, LightningSpec, RetentionSpec, XieluMLPSpec,
                     HeadSpec, MixerSpec, ModelSpec, NormSpec, ParallelSpec, PolyNormMLPSpec, PositionSpec, RunSpec)
 from .projected import ProjectedMixer

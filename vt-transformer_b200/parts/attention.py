@@ -13,7 +13,9 @@ def _attention(spec, prefix, rt):
     """The attention mixer for a spec: the kernels of ``PagedAttention`` take the whole head rotated from a table,
     values as wide as keys and a causal or windowed mask; everything else runs ``GeneralAttention``."""
     plain = (spec.v_dim in (None, spec.head_dim) and spec.qk_norm_eps is None and spec.chunk is None
-             and spec.position.kind != "rotary_computed" and not spec.keep_first)
+             and spec.position.kind != "rotary_computed" and not spec.keep_first and spec.proj_norm_eps is None
+             and spec.q_temp is None and spec.softcap is None and spec.sink == "none" and spec.gate == "none"
+             and spec.weight_suffix == ".weight" and spec.bias_suffix == ".bias")
     return (PagedAttention if plain else GeneralAttention)(spec, prefix, rt)
 
 
@@ -104,15 +106,21 @@ class GeneralAttention(ProjectedMixer):
     """Grouped-query attention with the options that ``PagedAttention``'s kernels do not take: values of another size
     than keys (``v_dim``), a rotation of the first dimensions of a head only, with the angle formed where it is used
     (``rotary_computed``), q and k divided by their root mean square after the rotation (``qk_norm_eps``), and a mask
-    of chunks (``chunk``) beside or instead of the window.  One kernel rotates and norms q and k (32-bit) and stores
-    k and v into the pages; the attention kernel walks the visible keys of every (token, head) with a running maximum
-    and sum in 32-bit.  No biases."""
+    of chunks (``chunk``) beside or instead of the window; a norm of q and of k over all their heads together with a
+    weight, before the rotation (``proj_norm_eps``); a query temperature that grows with the position (``q_temp``); capped
+    scores (``softcap``); a sink in the softmax's denominator (``sink``); a gate on the heads' results, one number a head
+    or one an element, whose matrix joins the packed input product (``gate``); biases.  One kernel norms, rotates and
+    scales q and k (32-bit) and stores k and v into the pages; the attention kernel walks the visible keys of every
+    (token, head) with a running maximum and sum in 32-bit and ends with the sink and the gate."""
 
     def __init__(self, spec, prefix, rt):
         super().__init__(spec, prefix, rt)
-        if spec.qkv_bias or spec.out_bias:
-            raise ValueError("attention: biases are built for the plain attention only (rotation of the whole head, "
-                             "values as wide as keys, no norm of q and k, no chunks)")
+        if spec.sink not in ("none", "zero", "learned"):
+            raise ValueError(f"attention: sink '{spec.sink}' is not known; known: none, zero, learned")
+        if spec.gate not in ("none", "head", "element"):
+            raise ValueError(f"attention: gate '{spec.gate}' is not known; known: none, head, element")
+        if spec.proj_norm_eps is not None and spec.qk_norm_eps is not None:
+            raise ValueError("attention: a norm of q and k over the whole projection or head by head, not both")
         if spec.position.kind not in ("rotary_computed", "none"):
             raise ValueError(f"attention: position encoding '{spec.position.kind}' is not built beside the general options; "
                              f"known: rotary_computed, none")
@@ -129,20 +137,43 @@ class GeneralAttention(ProjectedMixer):
                            keep_first=s.keep_first if s.window else 0)
 
     def param_specs(self):
-        s, p, x = self.spec, self.prefix, self.spec.weight_suffix
+        s, p, x, bx = self.spec, self.prefix, self.spec.weight_suffix, self.spec.bias_suffix
         q, k, v, o = s.names
-        return {
-            f"{p}{q}{x}": ParamSpec((s.heads * s.head_dim, s.hidden)),
-            f"{p}{k}{x}": ParamSpec((s.kv_heads * s.head_dim, s.hidden)),
-            f"{p}{v}{x}": ParamSpec((s.kv_heads * self.v_dim, s.hidden)),
-            f"{p}{o}{x}": ParamSpec((s.hidden, s.heads * self.v_dim)),
-        }
+        sizes = {q: s.heads * s.head_dim, k: s.kv_heads * s.head_dim, v: s.kv_heads * self.v_dim}
+        out = {f"{p}{n}{x}": ParamSpec((size, s.hidden)) for n, size in sizes.items()}
+        out[f"{p}{o}{x}"] = ParamSpec((s.hidden, s.heads * self.v_dim))
+        if s.qkv_bias:
+            out.update({f"{p}{n}{bx}": ParamSpec((size,), role="vector") for n, size in sizes.items()})
+        if s.out_bias:
+            out[f"{p}{o}{bx}"] = ParamSpec((s.hidden,), role="vector")
+        if s.proj_norm_eps is not None:
+            out[p + s.norm_names[0]] = ParamSpec((sizes[q],), role="vector", init="one_plus_normal")
+            out[p + s.norm_names[1]] = ParamSpec((sizes[k],), role="vector", init="one_plus_normal")
+        if s.sink == "learned":
+            out[p + s.sink_name] = ParamSpec((s.heads,), role="vector")
+        if s.gate != "none":
+            out[p + s.gate_name] = ParamSpec((s.heads if s.gate == "head" else s.heads * self.v_dim, s.hidden))
+        return out
 
     def load(self, get) -> None:
-        s, p, rt, x = self.spec, self.prefix, self.rt, self.spec.weight_suffix
+        s, p, rt, x, bx = self.spec, self.prefix, self.rt, self.spec.weight_suffix, self.spec.bias_suffix
         q, k, v, o = s.names
         self._in = [rt.param(get(f"{p}{n}{x}")) for n in (q, k, v)]
+        self._in_bias = [rt.param(get(f"{p}{n}{bx}"), "vector") for n in (q, k, v)] if s.qkv_bias else [None, None, None]
+        if s.gate != "none":
+            self._in.append(rt.param(get(p + s.gate_name)))
+            self._in_bias.append(None)
         self.w_o = rt.param(get(f"{p}{o}{x}"))
+        self.b_o = rt.param(get(f"{p}{o}{bx}"), "vector") if s.out_bias else None
+        self.q_weight = self.k_weight = None
+        if s.proj_norm_eps is not None:
+            self.q_weight = rt.param(get(p + s.norm_names[0]), "vector")
+            self.k_weight = rt.param(get(p + s.norm_names[1]), "vector")
+        self.sinks = None
+        if s.sink == "learned":
+            self.sinks = rt.param(get(p + s.sink_name), "vector")
+        elif s.sink == "zero":
+            self.sinks = torch.zeros(s.heads, dtype=torch.float32, device=rt.device)
         self.position.load(get)
         self.pack()
 
@@ -152,19 +183,33 @@ class GeneralAttention(ProjectedMixer):
     def in_matrices(self):
         return list(self._in)
 
+    def in_biases(self):
+        return list(self._in_bias) if any(b is not None for b in self._in_bias) else None
+
     def out_matrix(self):
         return self.w_o
 
+    def out_bias(self):
+        return self.b_o
+
     def inner_size(self) -> int:
         return self.spec.heads * self.v_dim
+
+    def extra_weight_bytes(self) -> int:
+        return sum(4 * t.numel() for t in (self.q_weight, self.k_weight, self.sinks) if t is not None)
 
     def core(self, y, cols, ctx, cache, out, out_col, out_scale) -> None:
         s, ops = self.spec, self.rt.ops
         freq = getattr(self.position, "frequencies", None)
         k_pages, v_pages = cache.pages["k"], cache.pages["v"]
-        ops.attention_prepare(y, cols[0], cols[1], cols[2], ctx, freq, s.qk_norm_eps, k_pages, v_pages, cache.block_table,
-                              s.heads, s.kv_heads, s.head_dim, self.v_dim, store=cache.writes, status=ctx.status)
-        if cols[0] == 0 and not s.keep_first and ops.tensor_core_attention_takes(y.dtype, s.heads, s.kv_heads, s.head_dim, self.v_dim, cache.page_size):
+        whole = s.proj_norm_eps is not None
+        ops.attention_prepare(y, cols[0], cols[1], cols[2], ctx, freq, s.proj_norm_eps if whole else s.qk_norm_eps, k_pages, v_pages,
+                              cache.block_table, s.heads, s.kv_heads, s.head_dim, self.v_dim, store=cache.writes, status=ctx.status,
+                              q_weight=self.q_weight, k_weight=self.k_weight, norm_first=whole, whole_projection=whole,
+                              rot_mult=getattr(self.position, "mult", 1.0), q_temp=s.q_temp)
+        extras = s.softcap is not None or self.sinks is not None or s.gate != "none"
+        if (not extras and cols[0] == 0 and not s.keep_first
+                and ops.tensor_core_attention_takes(y.dtype, s.heads, s.kv_heads, s.head_dim, self.v_dim, cache.page_size)):
             # values as wide as keys at a head size the tensor-core kernels take: the kernels of the plain attention walk
             # the keys (tcgen05 for long portions, mma.sync tiles, the single-token kernel), with the chunks as one more
             # bound of the keys a row sees.  They write a tensor of their own, which is then scaled into its columns.
@@ -178,7 +223,8 @@ class GeneralAttention(ProjectedMixer):
             return
         ops.attention_general(y, cols[0], out, out_col, out_scale, k_pages, v_pages, ctx, cache.block_table, s.heads,
                               s.kv_heads, s.head_dim, self.v_dim, s.window, s.chunk, self.scale, status=ctx.status,
-                              keep_first=s.keep_first if s.window else 0)
+                              keep_first=s.keep_first if s.window else 0, sinks=self.sinks, softcap=s.softcap,
+                              gate=s.gate, gate_col=cols[3] if s.gate != "none" else 0)
 
 
 @register_part("mixer", "differential_attention")

@@ -22,23 +22,30 @@ class GatedMLP(FeedForward):
             raise ValueError(f"gated_mlp: activation '{spec.activation}' is not built; known: silu")
 
     def param_specs(self):
-        s, p = self.spec, self.prefix
+        s, p, x = self.spec, self.prefix, self.spec.weight_suffix
         g, u, d = s.names
         return {
-            f"{p}{g}.weight": ParamSpec((s.inter, s.hidden)),
-            f"{p}{u}.weight": ParamSpec((s.inter, s.hidden)),
-            f"{p}{d}.weight": ParamSpec((s.hidden, s.inter)),
+            f"{p}{g}{x}": ParamSpec((s.inter, s.hidden)),
+            f"{p}{u}{x}": ParamSpec((s.inter, s.hidden)),
+            f"{p}{d}{x}": ParamSpec((s.hidden, s.inter)),
         }
 
     def load(self, get) -> None:
-        s, p, rt = self.spec, self.prefix, self.rt
+        s, p, rt, x = self.spec, self.prefix, self.rt, self.spec.weight_suffix
         g, u, d = s.names
-        mats = [rt.param(get(f"{p}{n}.weight")) for n in (g, u)]
+        mats = [rt.param(get(f"{p}{n}{x}")) for n in (g, u)]
         if mats[0].dtype != mats[1].dtype:
             mats = [m.float() for m in mats]
+        self.w_down = rt.param(get(f"{p}{d}{x}"))
+        if s.inter % 8:
+            # an inner size that is no multiple of 8 is padded to one: rows of zeros in gate and up give silu(0) * 0 = 0,
+            # which meets columns of zeros in down
+            from .projected import pack_columns, pack_rows
+            mats = [pack_rows([m])[0] for m in mats]
+            self.w_down = pack_columns([self.w_down])[0]
+        self.inter = mats[0].shape[0]
         self.w_gate_up = rt.ops.interleave_gate_up(mats[0], mats[1])
         del mats
-        self.w_down = rt.param(get(f"{p}{d}.weight"))
 
     def weight_bytes(self) -> int:
         return (self.w_gate_up.numel() * self.w_gate_up.element_size()
@@ -50,7 +57,7 @@ class GatedMLP(FeedForward):
     def forward(self, h, ctx):
         s, ops = self.spec, self.rt.ops
         T = h.shape[0]
-        act = torch.empty((T, s.inter), dtype=h.dtype, device=h.device)
+        act = torch.empty((T, self.inter), dtype=h.dtype, device=h.device)
         ops.linear_silu_mul(h, self.w_gate_up, act, then=ops.product_hint(self.w_down, "stream"))
         return ops.linear_to_stream(act, self.w_down, None, then=self.then)
 

@@ -69,13 +69,23 @@ def rotation_frequencies(dim: int, base: float, scaling=None) -> torch.Tensor:
 class ComputedRotary(PositionEncoding):
     """The rotation of the first ``dim`` dimensions of a head, pairs (i, i + dim/2), by the angle
     position * base^(-2i/dim): the kernel that rotates forms the angle as a 32-bit product and takes its cos and sin
-    there, so there is no table and no limit of positions.  Holds the [dim/2] frequencies on the device."""
+    there, so there is no table and no limit of positions.  Holds the [dim/2] frequencies on the device.  With a
+    ``ramp`` the frequencies are those of ``ramped_frequencies`` and cos and sin are multiplied by ``mult``."""
 
     table = None
+    mult = 1.0
 
     def load(self, get) -> None:
-        self.frequencies = (rotation_frequencies(self.spec.dim, self.spec.base, self.spec.scaling).to(self.rt.device)
-                            if self.spec.dim else None)
+        self.frequencies, self.mult = None, 1.0
+        if not self.spec.dim:
+            return
+        if self.spec.ramp is not None:
+            if self.spec.scaling is not None:
+                raise ValueError("rotary_computed: either 'scaling' or 'ramp'")
+            f, self.mult = ramped_frequencies(self.spec.dim, self.spec.base, self.spec.ramp)
+            self.frequencies = f.to(self.rt.device)
+        else:
+            self.frequencies = rotation_frequencies(self.spec.dim, self.spec.base, self.spec.scaling).to(self.rt.device)
 
 
 def ramped_frequencies(dim: int, base: float, ramp=None):

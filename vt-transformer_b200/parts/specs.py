@@ -42,7 +42,7 @@ class PositionSpec:
     where l < original / high, divided by factor where l > original / low, and between the two it is
     (1 - s) f / factor + s f with s = (original / l - low) / (high - low).
     ``rotary_interleaved``: pairs (2i, 2i + 1) of the first ``dim`` dimensions, angle formed where it is used as for
-    ``rotary_computed``.  ``ramp`` = (factor, original, fast, slow): with n(t) = dim ln(original / (2 pi t)) / (2 ln base),
+    ``rotary_computed``.  ``ramp`` (``rotary_interleaved`` and ``rotary_computed``) = (factor, original, fast, slow): with n(t) = dim ln(original / (2 pi t)) / (2 ln base),
     lo = max(floor(n(fast)), 0), hi = min(ceil(n(slow)), dim - 1) and r_i = clamp((i - lo) / max(hi - lo, 0.001), 0, 1),
     pair i turns with f_i / factor * r_i + f_i (1 - r_i), and cos and sin are multiplied by 0.1 ln(factor) + 1."""
     dim: int = 0
@@ -80,6 +80,21 @@ class AttentionSpec(MixerSpec):
     qk_norm_eps: Optional[float] = None    # e: after the rotation q and k are divided, head by head, by sqrt(mean(.^2) + e)
     chunk: Optional[int] = None            # c: key j is seen from position p only if j // c == p // c (counted from position 0)
     keep_first: int = 0                    # n: beside the window's keys a token sees the keys at positions below n
+    bias_suffix: str = ".bias"             # appended to a projection's name for its bias
+    # e: before the rotation, all heads of q together (and of k) are divided by sqrt(mean(.^2) + e) over the whole
+    # projection and multiplied by a weight of that size (``norm_names`` below the part's prefix)
+    proj_norm_eps: Optional[float] = None
+    norm_names: Tuple[str, str] = ("q.norm", "k.norm")
+    q_temp: Optional[Tuple[float, int]] = None   # (c, n): q at position p is multiplied by 1 + c ln(floor((p + 1) / n) + 1)
+    softcap: Optional[float] = None        # c: score <- c tanh(score / c) after the scale
+    # "zero": the softmax's denominator holds one more term exp(0); "learned": exp(s_h), s [heads] the tensor ``sink_name``;
+    # the term has no key and no value and is neither scaled nor capped
+    sink: str = "none"
+    sink_name: str = "sink"
+    # "head": head h's result is multiplied by sigmoid(G h)_h, G [heads, hidden]; "element": the heads' results are
+    # multiplied element by element by sigmoid(G h), G [heads * v_dim, hidden]; G is the tensor ``gate_name``
+    gate: str = "none"
+    gate_name: str = "g"
     kind: str = "attention"
 
 
@@ -204,6 +219,67 @@ class DeltaRuleSpec(MixerSpec):
 
 
 @dataclass(frozen=True)
+class GatedDeltaSpec(MixerSpec):
+    """The delta rule with one decay a head.  q = Q h and k = K h have ``kv_heads`` heads of ``dim``, v = V h has ``heads``
+    heads of ``v_dim``; head h reads q/k head h // (heads / kv_heads).  Each of q, k, v passes a causal convolution over
+    time, channel by channel (``taps`` taps, the last one the present token's, zeros before a request's first token, no bias;
+    the tensor's name + ``conv_suffix``, [channels, taps]) and silu.  Then q and k are divided, head by head, by
+    sqrt(sum(.^2) + ``key_eps``) and q is multiplied by dim^(-1/2).  With beta = sigmoid(B h) and
+    g = exp(-exp(A_log[h]) softplus(A h + dt_bias[h])), one number a head each, and S [dim, v_dim] (32-bit, zero at the start
+    of a request): S <- g S; u = beta (v - S^T k); S <- S + k u^T; o = S^T q.  Each head's o is divided by its root mean
+    square (``norm_eps``), multiplied by a weight [v_dim] shared by the heads and by silu(G h); then the output projection.
+    A request keeps S and the last taps - 1 inputs of the convolutions.  ``names``: q, k, v, gate, output, the norm's
+    weight, B, A, A_log, dt_bias."""
+    hidden: int = 0
+    heads: int = 0
+    kv_heads: int = 0
+    dim: int = 0
+    v_dim: int = 0
+    taps: int = 1
+    key_eps: float = 1e-6
+    norm_eps: float = 1e-6
+    names: Tuple[str, ...] = ("q", "k", "v", "g", "o", "norm", "b", "a", "A_log", "dt_bias")
+    conv_suffix: str = ".conv"
+    kind: str = "gated_delta"
+
+
+@dataclass(frozen=True)
+class MatrixMemorySpec(MixerSpec):
+    """A matrix of memory a head with exponential gates.  q = Q h dim^(-1/2), k = K h (``heads`` heads of ``dim``), v = V h
+    (``v_dim``); the logarithms of the gates, one number a head: i = c tanh((I h + b_i) / c), f = log sigmoid(c tanh((F h + b_f) / c))
+    with c = ``gate_cap``.  With S [dim, v_dim], n [dim] and m (32-bit, all zero at the start of a request):
+    m' = max(f + m, i); S <- exp(f + m - m') S + exp(i - m') k v^T; n likewise with k alone; m <- m';
+    o = S^T q / (max(|n . q|, exp(-m)) + ``den_eps``).  Each head's o is divided by its root mean square (``norm_eps``); the heads
+    together are multiplied by a weight [heads * v_dim] and by sigmoid(G h); then the output projection.  ``names``: q, k, v,
+    gate, output, the norm's weight, I, F; a bias is the matrix's name + ``bias_suffix``."""
+    hidden: int = 0
+    heads: int = 0
+    dim: int = 0
+    v_dim: int = 0
+    gate_cap: float = 15.0
+    den_eps: float = 1e-6
+    norm_eps: float = 1e-6
+    names: Tuple[str, ...] = ("q", "k", "v", "g", "o", "norm", "i", "f")
+    bias_suffix: str = ".b"
+    kind: str = "matrix_memory"
+
+
+@dataclass(frozen=True)
+class NormedParallelSpec(MixerSpec):
+    """Several mixers side by side on the same input, each result normed before the sum:
+    sum_i scales[i] * w_i * y_i / sqrt(mean(y_i^2) + eps) with y_i = branches[i](h) after its own output projection and w_i
+    [hidden] the tensor ``norm_names[i]`` below the part's prefix.  ``prefixes[i]`` is appended to the part's prefix for
+    branch i's tensors."""
+    hidden: int = 0
+    branches: Tuple[MixerSpec, ...] = ()
+    scales: Tuple[float, ...] = ()
+    prefixes: Tuple[str, ...] = ()
+    norm_names: Tuple[str, ...] = ()
+    eps: float = 1e-6
+    kind: str = "parallel_normed"
+
+
+@dataclass(frozen=True)
 class ParallelSpec(MixerSpec):
     """Several mixers side by side on the same input: sum_i scales[i] * branches[i](h).  ``prefixes[i]`` is appended
     to the part's prefix for branch i's tensors."""
@@ -220,11 +296,12 @@ class FeedForwardSpec:
 
 @dataclass(frozen=True)
 class GatedMLPSpec(FeedForwardSpec):
-    """down(act(gate(x)) * up(x)), no biases."""
+    """down(act(gate(x)) * up(x)), no biases.  ``weight_suffix`` is appended to a projection's name for its matrix."""
     hidden: int = 0
     inter: int = 0
     activation: str = "silu"
     names: Tuple[str, str, str] = ("gate_proj", "up_proj", "down_proj")
+    weight_suffix: str = ".weight"
     kind: str = "gated_mlp"
 
 
@@ -318,10 +395,12 @@ class RunSpec:
     run with ``writes=False`` reads a slot that an earlier run wrote (shared keys and
     values) and stores nothing.  A block may appear in several runs, each with a slot of
     its own.  For a block whose mixer keeps several things (``Mixer.cache_spec`` returns a tuple) ``cache`` is a tuple
-    of slots, one for each, in that order."""
+    of slots, one for each, in that order.  ``add_embedding``: before this run the embedding's output (the stream as it
+    was before the first run) is added to the stream once more."""
     block: int
     cache: object               # None, a slot, or a tuple of slots
     writes: bool = True
+    add_embedding: bool = False
 
 
 @dataclass(frozen=True)
