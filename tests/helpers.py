@@ -121,6 +121,9 @@ def plain_module(folder: str):
     if c.get("architecture") == "Geponex":
         from plain import geponex_plain
         return geponex_plain
+    if c.get("architecture") == "Fosepel":
+        from plain import fosepel_plain
+        return fosepel_plain
     if c.get("architecture") == "Vegilix":
         from plain import vegilix_plain
         return vegilix_plain

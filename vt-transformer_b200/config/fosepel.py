@@ -147,8 +147,8 @@ class FosepelConfig(ModelConfig):
                     raise ConfigError(f"{at}: right: 'heads' {m.heads} is not a multiple of 'kv_heads' {m.kv_heads}")
                 if not 1 <= m.conv <= 16:
                     raise ConfigError(f"{at}: right: 'conv' {m.conv} taps are not supported (1 to 16)")
-            if m is not None and (m.dim > 512 or m.vdim > 8192):
-                raise ConfigError(f"{at}: right: 'dim' above 512 is not supported by the scan kernel")
+            if m is not None and m.dim > 256:
+                raise ConfigError(f"{at}: right: 'dim' above 256 is not supported by the scan kernel")
             if isinstance(m, FosepelMemory) and not m.gate_cap > 0:
                 raise ConfigError(f"{at}: right: 'gate_cap' must be positive")
 

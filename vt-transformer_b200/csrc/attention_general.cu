@@ -2,7 +2,8 @@
 // the angle formed where it is used, q and k divided by their root mean square after the rotation, and a mask of
 // chunks beside the causal one and the window, first tokens that stay visible beside a window, a norm of q and k with a
 // weight before the rotation, and two maps of queries and keys a head over one set of values whose results are
-// subtracted and normed (differential attention).
+// subtracted and normed (differential attention); a norm of q and of k over all their heads together, a query
+// temperature that grows with the position, capped scores, a sink in the denominator and a gate on a head's result.
 //
 // Two kernels.  `attention_prepare` (one block a token, one warp a head): rotation of pairs (i, i + half) by
 // position * frequency[i] (a 32-bit product, precise sine and cosine), the norm over the head in 32-bit, q written
@@ -28,8 +29,9 @@ attention_prepare_kernel(T* __restrict__ y, int stride, int q_col, int k_col, in
                          T* __restrict__ k_cache, T* __restrict__ v_cache, const int* __restrict__ block_table,
                          int table_stride, int n_seqs, int n_pages, int heads, int kv_heads, int dim, int v_dim,
                          int page_size, int store, int* status, int v_heads, const float* __restrict__ q_weight,
-                         const float* __restrict__ k_weight, int norm_first) {
+                         const float* __restrict__ k_weight, int norm_first, int whole, float rot_mult, float qt_coef, int qt_every) {
     __shared__ float head[kPrepareWarps][32 * kMaxPerLane];
+    __shared__ float scratch[32];
     pdl_launch();
     const int t = blockIdx.x;
     const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
@@ -55,13 +57,30 @@ attention_prepare_kernel(T* __restrict__ y, int stride, int q_col, int k_col, in
     const int slot = pos % page_size;
     const int units = heads + (store ? kv_heads : 0);
     float* hv = head[warp];
+    // the norm over the whole projection: one mean square over all heads of q, one over all heads of k (the block is
+    // one token's, so every thread is here)
+    float whole_q = 1.f, whole_k = 1.f;
+    if (whole && norm_eps >= 0.f) {
+        float sq = 0.f, sk = 0.f;
+        for (int e = threadIdx.x; e < heads * dim; e += blockDim.x) { const float v = to_float(row[q_col + e]); sq = fmaf(v, v, sq); }
+        for (int e = threadIdx.x; e < kv_heads * dim; e += blockDim.x) { const float v = to_float(row[k_col + e]); sk = fmaf(v, v, sk); }
+        whole_q = rsqrtf(block_sum(sq, scratch) / (float)(heads * dim) + norm_eps);
+        whole_k = rsqrtf(block_sum(sk, scratch) / (float)(kv_heads * dim) + norm_eps);
+    }
+    // the query's temperature: 1 + c ln(floor((p + 1) / n) + 1)
+    const float q_times = qt_coef != 0.f ? 1.f + qt_coef * logf((float)((pos + 1) / qt_every) + 1.f) : 1.f;
     for (int u = warp; u < units; u += kPrepareWarps) {
         const bool is_q = u < heads;
         T* src = is_q ? row + q_col + u * dim : row + k_col + (u - heads) * dim;
         for (int i = lane; i < dim; i += 32) hv[i] = to_float(src[i]);
         __syncwarp();
-        const float* w = is_q ? q_weight : k_weight;           // the norm's weight [dim], or none
-        if (norm_first && norm_eps >= 0.f) {
+        const float* w = is_q ? q_weight : k_weight;           // the norm's weight [dim] (or none); [all heads * dim] with whole
+        if (whole && norm_eps >= 0.f) {
+            const float sc = is_q ? whole_q : whole_k;
+            const float* wh = w ? w + (size_t)(is_q ? u : u - heads) * dim : nullptr;
+            for (int i = lane; i < dim; i += 32) hv[i] = hv[i] * sc * (wh ? wh[i] : 1.f);
+            __syncwarp();
+        } else if (norm_first && norm_eps >= 0.f) {
             // the norm comes before the rotation: the head is normed where it lies, then turned
             float s0 = 0.f;
             for (int i = lane; i < dim; i += 32) s0 = fmaf(hv[i], hv[i], s0);
@@ -82,6 +101,8 @@ attention_prepare_kernel(T* __restrict__ y, int stride, int q_col, int k_col, in
                     const float angle = (float)pos * freq[f];
                     float sn, cs;
                     sincosf(angle, &sn, &cs);
+                    sn *= rot_mult;
+                    cs *= rot_mult;
                     v = i < half ? v * cs - hv[i + half] * sn : v * cs + hv[i - half] * sn;
                 }
             }
@@ -89,8 +110,9 @@ attention_prepare_kernel(T* __restrict__ y, int stride, int q_col, int k_col, in
             ss = fmaf(v, v, ss);
         }
         float scale = 1.f;
-        const bool after = !norm_first && norm_eps >= 0.f;
+        const bool after = !norm_first && !whole && norm_eps >= 0.f;
         if (after) scale = rsqrtf(warp_sum(ss) / (float)dim + norm_eps);
+        if (is_q) scale *= q_times;
         T* dst = is_q ? src : k_cache + (((size_t)page * kv_heads + (u - heads)) * page_size + slot) * dim;
 #pragma unroll
         for (int r = 0; r < kMaxPerLane; ++r) {
@@ -111,18 +133,19 @@ cudaError_t launch_attention_prepare(int dtype, void* y, int stride, int q_col, 
                                      void* v_cache, const int* block_table, int table_stride, int n_seqs, int n_pages,
                                      int n_tokens, int heads, int kv_heads, int dim, int v_dim, int page_size, int store,
                                      int* status, int v_heads, const float* q_weight, const float* k_weight, int norm_first,
-                                     cudaStream_t stream) {
+                                     cudaStream_t stream, int whole, float rot_mult, float qt_coef, int qt_every) {
     if (n_tokens == 0) return cudaSuccess;
+    if (qt_every < 1) return cudaErrorInvalidValue;
     if (dim > 32 * kMaxPerLane || 2 * half > dim) return cudaErrorInvalidValue;
     if (dtype == kBF16)
         return launch(attention_prepare_kernel<__nv_bfloat16>, n_tokens, 32 * kPrepareWarps, 0, stream, (__nv_bfloat16*)y, stride,
                       q_col, k_col, v_col, positions, token_seq, freq, half, norm_eps, (__nv_bfloat16*)k_cache,
                       (__nv_bfloat16*)v_cache, block_table, table_stride, n_seqs, n_pages, heads, kv_heads, dim, v_dim,
-                      page_size, store, status, v_heads, q_weight, k_weight, norm_first);
+                      page_size, store, status, v_heads, q_weight, k_weight, norm_first, whole, rot_mult, qt_coef, qt_every);
     return launch(attention_prepare_kernel<float>, n_tokens, 32 * kPrepareWarps, 0, stream, (float*)y, stride, q_col, k_col,
                   v_col, positions, token_seq, freq, half, norm_eps, (float*)k_cache, (float*)v_cache, block_table,
                   table_stride, n_seqs, n_pages, heads, kv_heads, dim, v_dim, page_size, store, status, v_heads, q_weight, k_weight,
-                  norm_first);
+                  norm_first, whole, rot_mult, qt_coef, qt_every);
 }
 
 // One warp for a (token, head).  The visible keys are taken 32 at a time, a lane a key: the lane forms its key's whole
@@ -144,7 +167,8 @@ attention_general_kernel(const T* __restrict__ y, int stride, int q_col, T* __re
                          const int* __restrict__ positions, const int* __restrict__ token_seq,
                          const int* __restrict__ block_table, int table_stride, int n_seqs, int n_pages, int n_tokens,
                          int heads, int kv_heads, int dim, int v_dim, int page_size, int window, int chunk, float scale,
-                         int* status, int keep_first, float lam, float sub_eps, const float* __restrict__ sinks, int v_stride) {
+                         int* status, int keep_first, float lam, float sub_eps, const float* __restrict__ sinks, int v_stride,
+                         float softcap, int gate_mode, int gate_col) {
     extern __shared__ __align__(16) float qs_all[];
     constexpr int kMaxPerLane = PL;
     pdl_launch();
@@ -222,6 +246,7 @@ attention_general_kernel(const T* __restrict__ y, int stride, int q_col, T* __re
                     for (int i = 0; i < dim; ++i) part4[i & 3] = fmaf(qm[i], to_float(kp[i]), part4[i & 3]);
                 }
                 s[m] = (part4[0] + part4[1]) + (part4[2] + part4[3]);
+                if (softcap > 0.f) s[m] = softcap * tanhf(s[m] / softcap);
             }
             float p[MAPS];
 #pragma unroll
@@ -260,11 +285,18 @@ attention_general_kernel(const T* __restrict__ y, int stride, int q_col, T* __re
             keep = expf(mx[0] - top);
             den = sum[0] * keep + expf(sk - top);
         }
-        const float inv = den > 0.f ? out_scale * keep / den : 0.f;
+        float inv = den > 0.f ? out_scale * keep / den : 0.f;
+        // the gate on the head's result: one number a head, or one an element, sigmoid of a column of y
+        const T* gp = y + (size_t)t * stride + gate_col;
+        if (gate_mode == 1) inv *= 1.f / (1.f + expf(-to_float(gp[h])));
 #pragma unroll
         for (int r = 0; r < kMaxPerLane; ++r) {
             const int i = lane + 32 * r;
-            if (i < v_dim) o[i] = from_float<T>(acc[0][r] * inv);
+            if (i < v_dim) {
+                float v = acc[0][r] * inv;
+                if (gate_mode == 2) v *= 1.f / (1.f + expf(-to_float(gp[(size_t)h * v_dim + i])));
+                o[i] = from_float<T>(v);
+            }
         }
         return;
     }
@@ -293,7 +325,8 @@ static cudaError_t launch_attention_general_t(const T* y, int stride, int q_col,
                                               const int* block_table, int table_stride, int n_seqs, int n_pages, int n_tokens,
                                               int heads, int kv_heads, int dim, int v_dim, int page_size, int window, int chunk,
                                               float scale, int* status, int keep_first, int maps, float lam, float sub_eps,
-                                              const float* sinks, int v_stride, cudaStream_t stream) {
+                                              const float* sinks, int v_stride, cudaStream_t stream, float softcap, int gate_mode,
+                                              int gate_col) {
     const long long pairs = (long long)n_tokens * heads;
     const int blocks = (int)((pairs + 3) / 4);
     // a key's row is read in 16-byte pieces where every row starts on such a boundary
@@ -305,7 +338,7 @@ static cudaError_t launch_attention_general_t(const T* y, int stride, int q_col,
     const size_t bytes = (size_t)4 * maps * ((dim + 3) & ~3) * sizeof(float);
     return launch(kernel, blocks, 128, bytes, stream, y, stride, q_col, out, out_stride, out_col, out_scale, k_cache, v_cache, positions,
                   token_seq, block_table, table_stride, n_seqs, n_pages, n_tokens, heads, kv_heads, dim, v_dim, page_size, window,
-                  chunk, scale, status, keep_first, lam, sub_eps, sinks, v_stride > 0 ? v_stride : v_dim);
+                  chunk, scale, status, keep_first, lam, sub_eps, sinks, v_stride > 0 ? v_stride : v_dim, softcap, gate_mode, gate_col);
 }
 
 cudaError_t launch_attention_general(int dtype, const void* y, int stride, int q_col, void* out, int out_stride, int out_col,
@@ -313,8 +346,10 @@ cudaError_t launch_attention_general(int dtype, const void* y, int stride, int q
                                      const int* token_seq, const int* block_table, int table_stride, int n_seqs, int n_pages,
                                      int n_tokens, int heads, int kv_heads, int dim, int v_dim, int page_size, int window,
                                      int chunk, float scale, int* status, int keep_first, int maps, float lam, float sub_eps,
-                                     cudaStream_t stream, const float* sinks, int v_stride) {
+                                     cudaStream_t stream, const float* sinks, int v_stride, float softcap, int gate_mode,
+                                     int gate_col) {
     if (n_tokens == 0) return cudaSuccess;
+    if ((softcap > 0.f || gate_mode != 0) && maps != 1) return cudaErrorInvalidValue;
     // keys of any size up to what four queries take of shared memory; values up to 256 numbers (two maps) or 1,024 (one)
     if (dim > 2048 || v_dim > 32 * (maps == 2 ? kMaxPerLane : kWidePerLane) || (maps != 1 && maps != 2)) return cudaErrorInvalidValue;
     if (sinks != nullptr && maps != 1) return cudaErrorInvalidValue;
@@ -322,11 +357,12 @@ cudaError_t launch_attention_general(int dtype, const void* y, int stride, int q
         return launch_attention_general_t((const __nv_bfloat16*)y, stride, q_col, (__nv_bfloat16*)out, out_stride, out_col, out_scale,
                                           (const __nv_bfloat16*)k_cache, (const __nv_bfloat16*)v_cache, positions, token_seq,
                                           block_table, table_stride, n_seqs, n_pages, n_tokens, heads, kv_heads, dim, v_dim,
-                                          page_size, window, chunk, scale, status, keep_first, maps, lam, sub_eps, sinks, v_stride, stream);
+                                          page_size, window, chunk, scale, status, keep_first, maps, lam, sub_eps, sinks, v_stride, stream,
+                                          softcap, gate_mode, gate_col);
     return launch_attention_general_t((const float*)y, stride, q_col, (float*)out, out_stride, out_col, out_scale, (const float*)k_cache,
                                       (const float*)v_cache, positions, token_seq, block_table, table_stride, n_seqs, n_pages,
                                       n_tokens, heads, kv_heads, dim, v_dim, page_size, window, chunk, scale, status, keep_first,
-                                      maps, lam, sub_eps, sinks, v_stride, stream);
+                                      maps, lam, sub_eps, sinks, v_stride, stream, softcap, gate_mode, gate_col);
 }
 
 }  // namespace vtb

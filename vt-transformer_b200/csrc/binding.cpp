@@ -229,6 +229,110 @@ void delta_scan(const Tensor& y, int64_t r_col, int64_t k_col, int64_t v_col, in
                                         rows.numel(), o.data_ptr<float>(), heads, dim, (int)most_threads, status_ptr(status), stream_of(y)), "delta_scan");
 }
 
+void check_gated(const Tensor& y, const Tensor& state, const Tensor& cu_q, const Tensor& rows, const Tensor& o, int64_t heads,
+                 int64_t v_dim, const char* who) {
+    check_cuda(y, "y"); check_f32(state, "state"); check_i32(cu_q, "cu_q"); check_i32(rows, "rows"); check_f32(o, "o");
+    TORCH_CHECK(y.dim() == 2 && o.dim() == 2 && o.size(0) == y.size(0) && o.size(1) == heads * v_dim, who, ": o must be [tokens, heads * v_dim]");
+    TORCH_CHECK(cu_q.numel() == rows.numel() + 1, who, ": cu_q has one entry more than rows");
+}
+
+void gated_delta_scan(const Tensor& y, int64_t q_col, int64_t k_col, int64_t v_col, int64_t b_col, int64_t a_col, const Tensor& conv_q,
+                      const Tensor& conv_k, const Tensor& conv_v, const Tensor& a_log, const Tensor& dt_bias, double key_eps, double q_scale,
+                      Tensor& state, c10::optional<Tensor> tail, const Tensor& cu_q, const Tensor& rows, Tensor& o, int64_t heads,
+                      int64_t kv_heads, int64_t dim, int64_t v_dim, c10::optional<Tensor> status, int64_t most_threads) {
+    check_gated(y, state, cu_q, rows, o, heads, v_dim, "gated_delta_scan");
+    TORCH_CHECK(state.dim() == 4 && state.size(1) == heads && state.size(2) == dim && state.size(3) == v_dim,
+                "gated_delta_scan: state must be [rows, heads, dim, v_dim]");
+    TORCH_CHECK(kv_heads >= 1 && heads % kv_heads == 0, "gated_delta_scan: heads a multiple of kv_heads");
+    check_f32(conv_q, "conv_q"); check_f32(conv_k, "conv_k"); check_f32(conv_v, "conv_v"); check_f32(a_log, "a_log"); check_f32(dt_bias, "dt_bias");
+    const int64_t nq = kv_heads * dim, nv = heads * v_dim;
+    TORCH_CHECK(conv_q.dim() == 2 && conv_k.dim() == 2 && conv_v.dim() == 2 && conv_q.size(0) == nq && conv_k.size(0) == nq && conv_v.size(0) == nv,
+                "gated_delta_scan: the convolutions' weights are [channels, taps]");
+    const int64_t taps = conv_q.size(1);
+    TORCH_CHECK(taps >= 1 && taps <= 16 && conv_k.size(1) == taps && conv_v.size(1) == taps, "gated_delta_scan: 1 to 16 taps, the same for q, k and v");
+    TORCH_CHECK(a_log.numel() == heads && dt_bias.numel() == heads, "gated_delta_scan: a_log and dt_bias [heads]");
+    const float* tp = nullptr;
+    if (taps > 1) {
+        TORCH_CHECK(tail.has_value(), "gated_delta_scan: more than one tap needs the kept inputs");
+        check_f32(*tail, "tail");
+        TORCH_CHECK(tail->dim() == 3 && tail->size(0) == state.size(0) && tail->size(1) == taps - 1 && tail->size(2) == 2 * nq + nv,
+                    "gated_delta_scan: tail must be [rows, taps - 1, channels of q, k and v]");
+        tp = tail->data_ptr<float>();
+    }
+    check_cols(y, q_col, nq, "gated_delta_scan (q)"); check_cols(y, k_col, nq, "gated_delta_scan (k)"); check_cols(y, v_col, nv, "gated_delta_scan (v)");
+    check_cols(y, b_col, heads, "gated_delta_scan (beta)"); check_cols(y, a_col, heads, "gated_delta_scan (decay)");
+    TORCH_CHECK(dim <= 512, "gated_delta_scan: head sizes up to 512");
+    c10::cuda::CUDAGuard guard(y.device());
+    check_launch(vtb::launch_gated_delta_scan(dtype_code(y, "y"), y.data_ptr(), y.size(1), q_col, k_col, v_col, b_col, a_col,
+                                              conv_q.data_ptr<float>(), conv_k.data_ptr<float>(), conv_v.data_ptr<float>(), taps,
+                                              a_log.data_ptr<float>(), dt_bias.data_ptr<float>(), (float)key_eps, (float)q_scale,
+                                              state.data_ptr<float>(), state.size(0), tp, cu_q.data_ptr<int>(), rows.data_ptr<int>(),
+                                              rows.numel(), o.data_ptr<float>(), heads, kv_heads, dim, v_dim, (int)most_threads,
+                                              status_ptr(status), stream_of(y)), "gated_delta_scan");
+}
+
+void conv_tail_update(const Tensor& y, std::vector<int64_t> cols, std::vector<int64_t> widths, Tensor& tail, const Tensor& cu_q,
+                      const Tensor& rows, c10::optional<Tensor> status) {
+    check_cuda(y, "y"); check_f32(tail, "tail"); check_i32(cu_q, "cu_q"); check_i32(rows, "rows");
+    TORCH_CHECK(y.dim() == 2 && tail.dim() == 3 && cols.size() == widths.size() && cols.size() >= 1 && cols.size() <= 4,
+                "conv_tail_update: y [tokens, .], tail [rows, kept, channels], one to four groups of columns");
+    int c[4] = {0, 0, 0, 0}, w[4] = {0, 0, 0, 0};
+    int64_t total = 0;
+    for (size_t i = 0; i < cols.size(); ++i) {
+        check_cols(y, cols[i], widths[i], "conv_tail_update");
+        c[i] = (int)cols[i]; w[i] = (int)widths[i]; total += widths[i];
+    }
+    TORCH_CHECK(total == tail.size(2) && tail.size(1) >= 1 && tail.size(1) <= 15, "conv_tail_update: the groups' widths add up to tail's channels; 1 to 15 kept inputs");
+    TORCH_CHECK(cu_q.numel() == rows.numel() + 1, "conv_tail_update: cu_q has one entry more than rows");
+    c10::cuda::CUDAGuard guard(y.device());
+    check_launch(vtb::launch_conv_tail_update(dtype_code(y, "y"), y.data_ptr(), y.size(1), c[0], w[0], c[1], w[1], c[2], w[2], c[3], w[3],
+                                              tail.data_ptr<float>(), tail.size(0), tail.size(1), tail.size(2), cu_q.data_ptr<int>(),
+                                              rows.data_ptr<int>(), rows.numel(), status_ptr(status), stream_of(y)), "conv_tail_update");
+}
+
+void memory_scan(const Tensor& y, int64_t q_col, int64_t k_col, int64_t v_col, int64_t i_col, int64_t f_col, const Tensor& i_bias,
+                 const Tensor& f_bias, double gate_cap, double q_scale, double den_eps, Tensor& state, const Tensor& cu_q, const Tensor& rows,
+                 Tensor& o, int64_t heads, int64_t dim, int64_t v_dim, c10::optional<Tensor> status, int64_t most_threads) {
+    check_gated(y, state, cu_q, rows, o, heads, v_dim, "memory_scan");
+    TORCH_CHECK(state.dim() == 4 && state.size(1) == heads && state.size(2) == dim + 1 && state.size(3) == v_dim + 1,
+                "memory_scan: state must be [rows, heads, dim + 1, v_dim + 1]");
+    check_f32(i_bias, "i_bias"); check_f32(f_bias, "f_bias");
+    TORCH_CHECK(i_bias.numel() == heads && f_bias.numel() == heads && gate_cap > 0.0, "memory_scan: the gates' biases [heads]; a positive cap");
+    check_cols(y, q_col, heads * dim, "memory_scan (q)"); check_cols(y, k_col, heads * dim, "memory_scan (k)");
+    check_cols(y, v_col, heads * v_dim, "memory_scan (v)"); check_cols(y, i_col, heads, "memory_scan (i)"); check_cols(y, f_col, heads, "memory_scan (f)");
+    TORCH_CHECK(dim <= 512, "memory_scan: head sizes up to 512");
+    c10::cuda::CUDAGuard guard(y.device());
+    Tensor snap = torch::empty({rows.numel(), heads, dim + 1}, state.options());
+    check_launch(vtb::launch_memory_scan(dtype_code(y, "y"), y.data_ptr(), y.size(1), q_col, k_col, v_col, i_col, f_col, i_bias.data_ptr<float>(),
+                                         f_bias.data_ptr<float>(), (float)gate_cap, (float)q_scale, (float)den_eps, state.data_ptr<float>(),
+                                         state.size(0), cu_q.data_ptr<int>(), rows.data_ptr<int>(), rows.numel(), o.data_ptr<float>(), heads,
+                                         dim, v_dim, (int)most_threads, status_ptr(status), stream_of(y), snap.data_ptr<float>()), "memory_scan");
+}
+
+void normed_sum(std::vector<Tensor> parts, std::vector<Tensor> weights, double eps, std::vector<double> scales, Tensor& out) {
+    check_f32(out, "out");
+    const size_t n = parts.size();
+    TORCH_CHECK(n >= 1 && n <= 4 && weights.size() == n && scales.size() == n && out.dim() == 2, "normed_sum: one to four parts, a weight and a scale each");
+    const float* pp[4] = {nullptr, nullptr, nullptr, nullptr};
+    const float* wp[4] = {nullptr, nullptr, nullptr, nullptr};
+    float sc[4] = {0.f, 0.f, 0.f, 0.f};
+    for (size_t i = 0; i < n; ++i) {
+        check_f32(parts[i], "part"); check_f32(weights[i], "weight");
+        TORCH_CHECK(parts[i].sizes() == out.sizes() && weights[i].numel() == out.size(1), "normed_sum: parts [tokens, width] like out, weights [width]");
+        pp[i] = parts[i].data_ptr<float>(); wp[i] = weights[i].data_ptr<float>(); sc[i] = (float)scales[i];
+    }
+    c10::cuda::CUDAGuard guard(out.device());
+    check_launch(vtb::launch_normed_sum((int)n, pp[0], pp[1], pp[2], pp[3], wp[0], wp[1], wp[2], wp[3], sc[0], sc[1], sc[2], sc[3], (float)eps,
+                                        out.data_ptr<float>(), out.size(0), out.size(1), stream_of(out)), "normed_sum");
+}
+
+void add_rows(Tensor& x, const Tensor& other) {
+    check_f32(x, "x"); check_f32(other, "other");
+    TORCH_CHECK(x.sizes() == other.sizes(), "add_rows: two tensors of one shape");
+    c10::cuda::CUDAGuard guard(x.device());
+    check_launch(vtb::launch_add_rows(x.data_ptr<float>(), other.data_ptr<float>(), x.numel(), stream_of(x)), "add_rows");
+}
+
 void check_pages(const Tensor& k_cache, const Tensor& v_cache, const Tensor& ref, int kv_heads, int dim, int v_dim, int v_heads = -1) {
     check_cuda(k_cache, "k_cache"); check_cuda(v_cache, "v_cache");
     if (v_heads < 0) v_heads = kv_heads;
@@ -243,7 +347,8 @@ void check_pages(const Tensor& k_cache, const Tensor& v_cache, const Tensor& ref
 void attention_prepare(Tensor& y, int64_t q_col, int64_t k_col, int64_t v_col, const Tensor& positions, const Tensor& token_seq,
                        c10::optional<Tensor> frequencies, double norm_eps, Tensor& k_cache, Tensor& v_cache, const Tensor& block_table,
                        int64_t heads, int64_t kv_heads, int64_t dim, int64_t v_dim, bool store, c10::optional<Tensor> status,
-                       int64_t v_heads, c10::optional<Tensor> q_weight, c10::optional<Tensor> k_weight, bool norm_first) {
+                       int64_t v_heads, c10::optional<Tensor> q_weight, c10::optional<Tensor> k_weight, bool norm_first,
+                       bool whole_projection, double rot_mult, double q_temp_coef, int64_t q_temp_every) {
     check_cuda(y, "y"); check_i32(positions, "positions"); check_i32(token_seq, "token_seq"); check_i32(block_table, "block_table");
     TORCH_CHECK(y.dim() == 2 && positions.numel() == y.size(0) && token_seq.numel() == y.size(0), "attention_prepare: one position and sequence a token");
     TORCH_CHECK(block_table.dim() == 2, "attention_prepare: block_table must be [sequences, stride]");
@@ -253,8 +358,11 @@ void attention_prepare(Tensor& y, int64_t q_col, int64_t k_col, int64_t v_col, c
     check_pages(k_cache, v_cache, y, kv_heads, dim, v_dim, v_heads);
     const float* qw = nullptr;
     const float* kw = nullptr;
-    if (q_weight.has_value()) { check_f32(*q_weight, "q_weight"); TORCH_CHECK(q_weight->numel() == dim, "attention_prepare: q_weight [dim]"); qw = q_weight->data_ptr<float>(); }
-    if (k_weight.has_value()) { check_f32(*k_weight, "k_weight"); TORCH_CHECK(k_weight->numel() == dim, "attention_prepare: k_weight [dim]"); kw = k_weight->data_ptr<float>(); }
+    TORCH_CHECK(!whole_projection || norm_first, "attention_prepare: the norm over the whole projection comes before the rotation");
+    TORCH_CHECK(q_temp_every >= 1, "attention_prepare: q_temp_every must be at least 1");
+    const int64_t qn = whole_projection ? heads * dim : dim, kn = whole_projection ? kv_heads * dim : dim;
+    if (q_weight.has_value()) { check_f32(*q_weight, "q_weight"); TORCH_CHECK(q_weight->numel() == qn, "attention_prepare: q_weight [dim], or [heads * dim] over the whole projection"); qw = q_weight->data_ptr<float>(); }
+    if (k_weight.has_value()) { check_f32(*k_weight, "k_weight"); TORCH_CHECK(k_weight->numel() == kn, "attention_prepare: k_weight [dim], or [kv_heads * dim] over the whole projection"); kw = k_weight->data_ptr<float>(); }
     const float* fp = nullptr;
     int half = 0;
     if (frequencies.has_value()) {
@@ -269,14 +377,19 @@ void attention_prepare(Tensor& y, int64_t q_col, int64_t k_col, int64_t v_col, c
                                                token_seq.data_ptr<int>(), fp, half, (float)norm_eps, k_cache.data_ptr(), v_cache.data_ptr(),
                                                block_table.data_ptr<int>(), block_table.size(1), block_table.size(0), k_cache.size(0),
                                                y.size(0), heads, kv_heads, dim, v_dim, k_cache.size(2), store ? 1 : 0, status_ptr(status),
-                                               v_heads, qw, kw, norm_first ? 1 : 0, stream_of(y)), "attention_prepare");
+                                               v_heads, qw, kw, norm_first ? 1 : 0, stream_of(y), whole_projection ? 1 : 0, (float)rot_mult,
+                                               (float)q_temp_coef, (int)q_temp_every), "attention_prepare");
 }
 
 void attention_general(const Tensor& y, int64_t q_col, Tensor& out, int64_t out_col, double out_scale, const Tensor& k_cache,
                        const Tensor& v_cache, const Tensor& positions, const Tensor& token_seq, const Tensor& block_table, int64_t heads,
                        int64_t kv_heads, int64_t dim, int64_t v_dim, int64_t window, int64_t chunk, double scale, c10::optional<Tensor> status,
-                       int64_t keep_first, int64_t maps, double lam, double sub_eps, c10::optional<Tensor> sinks, bool values_in_keys) {
+                       int64_t keep_first, int64_t maps, double lam, double sub_eps, c10::optional<Tensor> sinks, bool values_in_keys,
+                       double softcap, int64_t gate_mode, int64_t gate_col) {
     check_cuda(y, "y"); check_cuda(out, "out"); check_i32(positions, "positions"); check_i32(token_seq, "token_seq");
+    TORCH_CHECK(gate_mode >= 0 && gate_mode <= 2 && softcap >= 0.0, "attention_general: gate_mode 0, 1 or 2; softcap not negative");
+    TORCH_CHECK((gate_mode == 0 && softcap == 0.0) || maps == 1, "attention_general: a gate or capped scores take one map");
+    if (gate_mode != 0) check_cols(y, gate_col, gate_mode == 1 ? heads : heads * v_dim, "attention_general (gate)");
     TORCH_CHECK(maps == 1 || maps == 2, "attention_general: one map of queries and keys a head, or two");
     const float* sp = nullptr;
     if (sinks.has_value()) {
@@ -305,7 +418,8 @@ void attention_general(const Tensor& y, int64_t q_col, Tensor& out, int64_t out_
                                                token_seq.data_ptr<int>(), block_table.data_ptr<int>(), block_table.size(1),
                                                block_table.size(0), k_cache.size(0), y.size(0), heads, kv_heads, dim, v_dim, k_cache.size(2),
                                                window, chunk, (float)scale, status_ptr(status), keep_first, maps, (float)lam,
-                                               (float)sub_eps, stream_of(y), sp, values_in_keys ? (int)dim : 0), "attention_general");
+                                               (float)sub_eps, stream_of(y), sp, values_in_keys ? (int)dim : 0, (float)softcap, (int)gate_mode,
+                                               (int)gate_col), "attention_general");
 }
 
 void attention_diff(const Tensor& y, int64_t q_col, Tensor& out, int64_t out_col, double out_scale, const Tensor& k_cache,
@@ -1078,12 +1192,19 @@ PYBIND11_MODULE(TORCH_EXTENSION_NAME, m) {
     m.def("attention_prepare", &attention_prepare, py::arg("y"), py::arg("q_col"), py::arg("k_col"), py::arg("v_col"), py::arg("positions"),
           py::arg("token_seq"), py::arg("frequencies"), py::arg("norm_eps"), py::arg("k_cache"), py::arg("v_cache"), py::arg("block_table"),
           py::arg("heads"), py::arg("kv_heads"), py::arg("dim"), py::arg("v_dim"), py::arg("store"), py::arg("status") = py::none(),
-          py::arg("v_heads") = -1, py::arg("q_weight") = py::none(), py::arg("k_weight") = py::none(), py::arg("norm_first") = false);
+          py::arg("v_heads") = -1, py::arg("q_weight") = py::none(), py::arg("k_weight") = py::none(), py::arg("norm_first") = false,
+          py::arg("whole_projection") = false, py::arg("rot_mult") = 1.0, py::arg("q_temp_coef") = 0.0, py::arg("q_temp_every") = 1);
     m.def("attention_general", &attention_general, py::arg("y"), py::arg("q_col"), py::arg("out"), py::arg("out_col"), py::arg("out_scale"),
           py::arg("k_cache"), py::arg("v_cache"), py::arg("positions"), py::arg("token_seq"), py::arg("block_table"), py::arg("heads"),
           py::arg("kv_heads"), py::arg("dim"), py::arg("v_dim"), py::arg("window"), py::arg("chunk"), py::arg("scale"),
           py::arg("status") = py::none(), py::arg("keep_first") = 0, py::arg("maps") = 1, py::arg("lam") = 0.0, py::arg("sub_eps") = 0.0,
-          py::arg("sinks") = py::none(), py::arg("values_in_keys") = false);
+          py::arg("sinks") = py::none(), py::arg("values_in_keys") = false, py::arg("softcap") = 0.0, py::arg("gate_mode") = 0,
+          py::arg("gate_col") = 0);
+    m.def("gated_delta_scan", &gated_delta_scan);
+    m.def("conv_tail_update", &conv_tail_update);
+    m.def("memory_scan", &memory_scan);
+    m.def("normed_sum", &normed_sum);
+    m.def("add_rows", &add_rows);
     m.def("attention_diff", &attention_diff);
     m.def("attention_diff_supports", &vtb::attention_diff_supports);
     m.def("attention_diff_tile_rows", &vtb::attention_diff_tile_rows);

@@ -35,6 +35,7 @@ SOURCES = [
     "attention_noalloc.cu",
     "sampling.cu",
     "recurrent.cu",
+    "recurrent_gated.cu",
     "attention_general.cu",
     "experts.cu",
     "attention_diff.cu",

@@ -58,26 +58,65 @@ cudaError_t launch_head_norm_gate(int dtype, const float* o, const void* y, int 
                                   int weight_per_channel, float eps, int act, void* out, int out_stride, int out_col,
                                   float out_scale, const int* token_seq, int n_tokens, int heads, int v_dim, cudaStream_t stream);
 
+// Recurrences with one decay a head (recurrent_gated.cu), in the manner of the scans above: q, k, v and the gates' inputs are
+// columns of y; the state is read at rows[sequence] and left as after the sequence's last token; out [tokens, heads * v_dim].
+// The delta rule with one decay a head: q and k [kv_heads * dim], v [heads * v_dim] pass a causal convolution over time
+// (conv_* [channels, taps], the last tap the present token's; the inputs before the step's first token from tail
+// [state_rows, taps - 1, 2 kv_heads dim + heads v_dim], oldest first; null with one tap) and silu; q and k are divided head
+// by head by sqrt(sum(.^2) + key_eps), q times q_scale; beta = sigmoid(y[b_col + h]), g = exp(-exp(a_log[h]) softplus(y[a_col + h]
+// + dt_bias[h])); S <- g S; u = beta (v - S^T k); S <- S + k u^T; o = S^T q.  state [state_rows, heads, dim, v_dim].
+cudaError_t launch_gated_delta_scan(int dtype, const void* y, int stride, int q_col, int k_col, int v_col, int b_col, int a_col,
+                                    const float* conv_q, const float* conv_k, const float* conv_v, int taps, const float* a_log,
+                                    const float* dt_bias, float key_eps, float q_scale, float* state, int state_rows, const float* tail,
+                                    const int* cu_q, const int* rows, int n_seqs, float* out, int heads, int kv_heads, int dim, int v_dim,
+                                    int most_threads, int* status, cudaStream_t stream);
+// tail [state_rows, kept, channels] takes the last `kept` inputs of every channel after the step (the step's last tokens, and
+// before them what it held); the channels are up to four groups of columns [c_i, c_i + w_i) of y, one after the other.
+cudaError_t launch_conv_tail_update(int dtype, const void* y, int stride, int c0, int w0, int c1, int w1, int c2, int w2, int c3, int w3,
+                                    float* tail, int state_rows, int kept, int channels, const int* cu_q, const int* rows, int n_seqs,
+                                    int* status, cudaStream_t stream);
+// The matrix memory with exponential gates: i = cap tanh((y[i_col + h] + i_bias[h]) / cap), f = log sigmoid(cap tanh((y[f_col + h] +
+// f_bias[h]) / cap)); m' = max(f + m, i); S <- exp(f + m - m') S + exp(i - m') k v^T, n likewise with k alone;
+// o = S^T q / (max(|n . q|, exp(-m')) + den_eps), q times q_scale.  state [state_rows, heads, dim + 1, v_dim + 1]: S beside n (the
+// last column), m at [dim, 0].
+cudaError_t launch_memory_scan(int dtype, const void* y, int stride, int q_col, int k_col, int v_col, int i_col, int f_col,
+                               const float* i_bias, const float* f_bias, float gate_cap, float q_scale, float den_eps, float* state,
+                               int state_rows, const int* cu_q, const int* rows, int n_seqs, float* out, int heads, int dim, int v_dim,
+                               int most_threads, int* status, cudaStream_t stream, float* snap);
+// (snap [sequences, heads, dim + 1]: scratch for n and m as they are before the step, used where a head's columns lie on several CTAs)
+// out = sum_i s_i w_i p_i / sqrt(mean(p_i^2) + eps), row by row, for n (1 to 4) float parts [tokens, width]; 32-bit.
+cudaError_t launch_normed_sum(int n, const float* p0, const float* p1, const float* p2, const float* p3, const float* w0, const float* w1,
+                              const float* w2, const float* w3, float s0, float s1, float s2, float s3, float eps, float* out,
+                              int n_tokens, int width, cudaStream_t stream);
+// x += other, element by element (float).
+cudaError_t launch_add_rows(float* x, const float* other, long long n, cudaStream_t stream);
+
 // The general attention (attention_general.cu).  Prepare: q [heads * dim] and k [kv_heads * dim] at their columns of y
 // are rotated (pairs (i, i + half) of each head's first 2 half dimensions, angle position * freq[i]) and, with
 // norm_eps >= 0, divided head by head by sqrt(mean(.^2) + norm_eps); q is written back, k and v [kv_heads * v_dim] go
 // into k_cache [pages, kv_heads, page_size, dim] and v_cache [pages, v_heads, page_size, v_dim] if store.  The norm
-// multiplies by q_weight / k_weight [dim] where given, and comes before the rotation with norm_first.
+// multiplies by q_weight / k_weight [dim] where given, and comes before the rotation with norm_first.  whole: the mean
+// square is over all heads of q together (and of k), the weights are [heads * dim] and [kv_heads * dim], before the
+// rotation.  rot_mult multiplies cos and sin.  qt_coef c != 0: q is multiplied by 1 + c ln((position + 1) / qt_every + 1)
+// (integer division), last of all.
 cudaError_t launch_attention_prepare(int dtype, void* y, int stride, int q_col, int k_col, int v_col, const int* positions,
                                      const int* token_seq, const float* freq, int half, float norm_eps, void* k_cache,
                                      void* v_cache, const int* block_table, int table_stride, int n_seqs, int n_pages,
                                      int n_tokens, int heads, int kv_heads, int dim, int v_dim, int page_size, int store,
                                      int* status, int v_heads, const float* q_weight, const float* k_weight, int norm_first,
-                                     cudaStream_t stream);
+                                     cudaStream_t stream, int whole = 0, float rot_mult = 1.f, float qt_coef = 0.f, int qt_every = 1);
 // Token t at position p sees keys j <= p with j > p - window or j < keep_first (window > 0) and j / chunk == p / chunk
 // (chunk > 0).  maps 2: q [heads, 2, dim], k_cache [pages, kv_heads * 2, page_size, dim], v_cache [pages, kv_heads, ..];
 // out = out_scale * o / sqrt(mean(o^2) + sub_eps) with o = a_1 - lam * a_2, the two maps' attentions over the same values.
+// softcap c > 0: a score becomes c tanh(score / c).  gate_mode 1: head h's result times sigmoid(y[t, gate_col + h]); 2: its
+// element i times sigmoid(y[t, gate_col + h v_dim + i]).
 cudaError_t launch_attention_general(int dtype, const void* y, int stride, int q_col, void* out, int out_stride, int out_col,
                                      float out_scale, const void* k_cache, const void* v_cache, const int* positions,
                                      const int* token_seq, const int* block_table, int table_stride, int n_seqs, int n_pages,
                                      int n_tokens, int heads, int kv_heads, int dim, int v_dim, int page_size, int window,
                                      int chunk, float scale, int* status, int keep_first, int maps, float lam, float sub_eps,
-                                     cudaStream_t stream, const float* sinks = nullptr, int v_stride = 0);
+                                     cudaStream_t stream, const float* sinks = nullptr, int v_stride = 0, float softcap = 0.f,
+                                     int gate_mode = 0, int gate_col = 0);
 
 // Attention over paged rows that all heads share (attention_latent.cu), bfloat16 on the tensor cores: head h's query
 // [key] at q_col + h * key of q; a row's first v_dim numbers are its value; out[t, out_col + h * v_dim + :].  sinks [heads]
