@@ -212,3 +212,11 @@ def greedy_generation(folder, name, device, dtype, n_new=12):
     llm.runner.cache.check()
     assert llm.stats["free_pages"] == [24] * len(llm.runner.cache.groups)
     return outs
+
+
+def within(got: torch.Tensor, folder, tokens, dtype, alone: bool = False) -> None:
+    """``got`` [T, vocab] against the plain logits of ``tokens``, position by position."""
+    ref = helpers.plain_logits(folder, tokens)
+    assert bool(torch.isfinite(got).all())
+    d = (got.double() - ref).abs().max(dim=1).values
+    assert float(d.max()) <= tol(dtype, ref, alone), (int(d.argmax()), float(d.max()), tol(dtype, ref, alone))

@@ -1,0 +1,372 @@
+"""Fosepel on the GPU: the kernels against the plain functions, every mechanism alone and the whole model, through the
+engine's step and entry point, against the plain implementation (tests/plain/fosepel_plain.py)."""
+import pytest
+import torch
+
+import helpers
+import fosepel_cases as cases
+from plain import fosepel_plain as plain
+
+pytestmark = pytest.mark.gpu
+DTYPES = ["bfloat16", "float32"]
+DEV = "cuda:0"
+F = torch.float64
+
+
+@pytest.fixture(scope="module")
+def fosepel_folders(tmp_path_factory):
+    made = {}
+
+    def get(name):
+        if name not in made:
+            made[name] = cases.make_folder(name, str(tmp_path_factory.mktemp(f"fosepel_{name}")))
+        return made[name]
+    return get
+
+
+def _logits(folder, tokens):
+    return helpers.plain_logits(folder, tokens)
+
+
+def _steps(lens_of_steps, rows, n_rows):
+    """Step contexts for sequences that go on from step to step in the state rows ``rows``."""
+    done = [0] * len(rows)
+    for lens in lens_of_steps:
+        ctx = helpers.step_context(lens, list(done), DEV)
+        ctx.rows = torch.tensor(rows, dtype=torch.int32, device=DEV)
+        yield ctx, lens
+        done = [d + n for d, n in zip(done, lens)]
+
+
+# ----------------------------------------------------------------------------- kernels against the plain functions
+
+
+@pytest.mark.parametrize("dtype", [torch.bfloat16, torch.float32])
+@pytest.mark.parametrize("heads,kv_heads,dim,v_dim,taps", [(4, 2, 12, 20, 4), (2, 2, 72, 40, 5), (1, 1, 16, 72, 1), (4, 2, 64, 128, 4),
+                                                           (2, 1, 136, 80, 3), (2, 2, 256, 64, 2), (3, 3, 32, 33, 2)])
+def test_gated_delta_scan_kernel(dtype, heads, kv_heads, dim, v_dim, taps):
+    """Three sequences through four steps (a long portion, portions shorter than the convolutions' reach, single tokens), the
+    state and the kept inputs carried in rows that are not in order, against the plain recurrence over each whole sequence."""
+    from vt_transformer_b200 import ops
+    g = torch.Generator().manual_seed(dim * 7 + v_dim)
+    nq, nv = kv_heads * dim, heads * v_dim
+    cols = [0, nq + 8, 2 * nq + 16, 2 * nq + nv + 24, 2 * nq + nv + 24 + 8 * (-(-heads // 8))]
+    width = cols[4] + 8 * (-(-heads // 8))
+    steps = [[40, 3, 17], [2, 1, 1], [1, 1, 1], [1, 2, 35]]
+    total = [sum(s[i] for s in steps) for i in range(3)]
+    ys = [torch.randn((n, width), generator=g).to(dtype) for n in total]
+    conv = [torch.randn((w, taps), generator=g) * 0.5 for w in (nq, nq, nv)]
+    a_log, dt_bias = torch.linspace(-3.0, 0.0, heads), torch.linspace(-1.0, 1.0, heads)
+    rows = [3, 0, 2]
+    state = torch.zeros((4, heads, dim, v_dim), device=DEV)
+    tail = torch.zeros((4, taps - 1, 2 * nq + nv), device=DEV) if taps > 1 else None
+    got, at = [[], [], []], [0, 0, 0]
+    for ctx, lens in _steps(steps, rows, 4):
+        y = torch.cat([ys[i][at[i]:at[i] + n] for i, n in enumerate(lens)]).to(DEV)
+        o = torch.full((y.shape[0], nv), float("nan"), device=DEV)
+        ops.gated_delta_scan(y, cols[0], cols[1], cols[2], cols[3], cols[4], *[c.to(DEV) for c in conv], a_log.to(DEV), dt_bias.to(DEV),
+                             1e-6, dim ** -0.5, state, tail, ctx, o, heads, kv_heads, dim, v_dim)
+        if tail is not None:
+            ops.conv_tail_update(y, cols[:3], (nq, nq, nv), tail, ctx)
+        off = 0
+        for i, n in enumerate(lens):
+            got[i].append(o[off:off + n].double().cpu())
+            off, at[i] = off + n, at[i] + n
+    assert float(state[1].abs().max()) == 0.0                          # a row of no sequence stays as it was
+    for i in range(3):
+        y = ys[i].double()
+        T = y.shape[0]
+        act = lambda x, w: plain.silu(plain.short_convolution(x, w.double()))
+        q = act(y[:, cols[0]:cols[0] + nq], conv[0]).view(T, kv_heads, dim)
+        k = act(y[:, cols[1]:cols[1] + nq], conv[1]).view(T, kv_heads, dim)
+        v = act(y[:, cols[2]:cols[2] + nv], conv[2]).view(T, heads, v_dim)
+        q = q / torch.sqrt((q * q).sum(-1, keepdim=True) + 1e-6) * dim ** -0.5
+        k = k / torch.sqrt((k * k).sum(-1, keepdim=True) + 1e-6)
+        beta = torch.sigmoid(y[:, cols[3]:cols[3] + heads])
+        decay = torch.exp(-torch.exp(a_log.double()) * plain.softplus(y[:, cols[4]:cols[4] + heads] + dt_bias.double()))
+        ref = plain.gated_delta_rule(q, k, v, beta, decay).reshape(T, nv)
+        err = float((torch.cat(got[i]) - ref).abs().max())
+        assert err <= 2e-5 * max(1.0, float(ref.abs().max())), (i, err)
+
+
+@pytest.mark.parametrize("dtype", [torch.bfloat16, torch.float32])
+@pytest.mark.parametrize("heads,dim,v_dim", [(3, 20, 24), (1, 136, 80), (2, 128, 128), (2, 28, 36), (2, 256, 520), (5, 16, 8)])
+def test_matrix_memory_scan_kernel(dtype, heads, dim, v_dim):
+    """As above for the matrix memory: the normalizer and the running maximum are carried beside the matrix (values of 520
+    columns put a head's columns on several CTAs, which all read the normalizer as it was before the step)."""
+    from vt_transformer_b200 import ops
+    g = torch.Generator().manual_seed(dim * 5 + v_dim)
+    nk, nv = heads * dim, heads * v_dim
+    cols = [0, nk + 8, 2 * nk + 16, 2 * nk + nv + 24, 2 * nk + nv + 24 + 8 * (-(-heads // 8))]
+    width = cols[4] + 8 * (-(-heads // 8))
+    steps = [[40, 3, 17], [2, 1, 1], [1, 1, 1], [1, 2, 35]]
+    total = [sum(s[i] for s in steps) for i in range(3)]
+    ys = [torch.randn((n, width), generator=g).to(dtype) for n in total]
+    for y in ys:                                                       # gates' inputs wide enough that the cap bites and the maximum moves
+        y[:, cols[3]:] = (y[:, cols[3]:].float() * 4.0).to(dtype)
+    i_bias, f_bias, cap = torch.linspace(-1.0, 1.5, heads), torch.linspace(1.0, 4.0, heads), 6.0
+    rows = [3, 0, 2]
+    state = torch.zeros((4, heads, dim + 1, v_dim + 1), device=DEV)
+    got, at = [[], [], []], [0, 0, 0]
+    for ctx, lens in _steps(steps, rows, 4):
+        y = torch.cat([ys[i][at[i]:at[i] + n] for i, n in enumerate(lens)]).to(DEV)
+        o = torch.full((y.shape[0], nv), float("nan"), device=DEV)
+        ops.memory_scan(y, cols[0], cols[1], cols[2], cols[3], cols[4], i_bias.to(DEV), f_bias.to(DEV), cap, dim ** -0.5, 1e-6, state, ctx, o,
+                        heads, dim, v_dim)
+        off = 0
+        for i, n in enumerate(lens):
+            got[i].append(o[off:off + n].double().cpu())
+            off, at[i] = off + n, at[i] + n
+    assert float(state[1].abs().max()) == 0.0
+    for i in range(3):
+        y = ys[i].double()
+        T = y.shape[0]
+        q = y[:, cols[0]:cols[0] + nk].view(T, heads, dim) * dim ** -0.5
+        k = y[:, cols[1]:cols[1] + nk].view(T, heads, dim)
+        v = y[:, cols[2]:cols[2] + nv].view(T, heads, v_dim)
+        ig = cap * torch.tanh((y[:, cols[3]:cols[3] + heads] + i_bias.double()) / cap)
+        fg = plain.log_sigmoid(cap * torch.tanh((y[:, cols[4]:cols[4] + heads] + f_bias.double()) / cap))
+        ref = plain.matrix_memory(q, k, v, ig, fg).reshape(T, nv)
+        err = float((torch.cat(got[i]) - ref).abs().max())
+        assert err <= 3e-5 * max(1.0, float(ref.abs().max())), (i, err)
+
+
+@pytest.mark.parametrize("width,parts", [(48, 2), (200, 3), (4104, 2), (72, 1), (64, 4)])
+def test_results_normed_before_they_are_added(width, parts):
+    from vt_transformer_b200 import ops
+    g = torch.Generator().manual_seed(width)
+    xs = [torch.randn((7, width), generator=g) * (i + 1) for i in range(parts)]
+    ws = [1.0 + 0.3 * torch.randn(width, generator=g) for _ in range(parts)]
+    scales = [0.5, 0.25, 1.5, -1.0][:parts]
+    out = torch.empty((7, width), device=DEV)
+    ops.normed_sum([x.to(DEV) for x in xs], [w.to(DEV) for w in ws], 1e-5, scales, out)
+    ref = sum(c * plain.rms(x.double(), 1e-5) * w.double() for x, w, c in zip(xs, ws, scales))
+    assert float((out.double().cpu() - ref).abs().max()) <= 2e-6 * max(1.0, float(ref.abs().max()))
+    x = torch.randn((5, width), generator=g)
+    xd = x.to(DEV)
+    ops.add_rows(xd, xs[0][:5].to(DEV))
+    assert torch.equal(xd.cpu(), x + xs[0][:5])
+
+
+# ----------------------------------------------------------------------------- every mechanism alone
+
+
+@pytest.mark.parametrize("dtype", DTYPES)
+@pytest.mark.parametrize("name", ["attention_alone", "parallel_alone", "parallel2_alone", "dense_alone"])
+def test_each_mechanism_alone(fosepel_folders, name, dtype):
+    folder = fosepel_folders(name)
+    prompts = cases.prompts_for(name, lengths=[1, 12, 45])
+    for family in ("whole", "tail", "portions"):
+        cases.replay(folder, prompts, family, DEV, dtype, alone=True)
+
+
+def test_the_sinks_count_once_unscaled_and_uncapped(fosepel_folders, tmp_path):
+    """The plain logits without the learned sinks, with sinks multiplied by the attention's scale and with capped sinks differ
+    from the model's far beyond the bound, as do those without the sink of score 0 (so a kernel that drops, scales or caps a
+    sink would show); the engine gives the model's."""
+    for name, key in (("parallel2_alone", "l0.mix.left.sink"), ("parallel_alone", None)):
+        folder = cases.rewritten(fosepel_folders(name), str(tmp_path / f"{name}_sharp"), lambda t: cases.sharpen_attention(t, 3.0))
+        ids = cases.prompts_for(name, lengths=[40])[0]
+        ref = _logits(folder, ids)
+        if key is not None:
+            left = cases.CONFIGS[name]["layers"][0]["mixer"]["left"]
+            changes = {"none": lambda t: t.__setitem__(key, torch.full_like(t[key], -30.0)),
+                       "scaled": lambda t: t.__setitem__(key, (t[key].float() * left["scale"]).to(t[key].dtype)),
+                       "capped": lambda t: t.__setitem__(key, (left["softcap"] * torch.tanh(t[key].float() * 4 / left["softcap"])).to(t[key].dtype))}
+            for n, change in changes.items():
+                if n == "capped":                # sinks large enough that a cap would bite
+                    big = cases.rewritten(folder, str(tmp_path / "big"), lambda t: t.__setitem__(key, (t[key].float() * 4).to(t[key].dtype)))
+                    assert float((_logits(cases.rewritten(big, str(tmp_path / n), lambda t: t.__setitem__(
+                        key, (left["softcap"] * torch.tanh(t[key].float() / left["softcap"])).to(t[key].dtype))), ids) - _logits(big, ids)).abs().max()) \
+                        > 3 * cases.tol("bfloat16", ref, alone=True)
+                    continue
+                other = _logits(cases.rewritten(folder, str(tmp_path / n), change), ids)
+                assert float((other - ref).abs().max()) > 3 * cases.tol("bfloat16", ref, alone=True), n
+        else:
+            # the same attention without its sink: the plain function with and without the term
+            q = torch.randn((6, 2, 8), dtype=F)
+            a = plain.causal_softmax_attention(q, q, q, 1.0, sink=torch.zeros(2, dtype=F))
+            b = plain.causal_softmax_attention(q, q, q, 1.0)
+            assert float((a - b).abs().max()) > 0.05
+        for dtype in DTYPES:
+            runner = cases.runner_for(folder, DEV, dtype, num_pages=4, max_requests=1)
+            for cuts in ([40], [30, 1], [2]):
+                row = runner.admit()
+                got = cases.step_all(runner, row, ids, cuts)
+                runner.release(row)
+                assert float((got - ref).abs().max()) <= cases.tol(dtype, ref, alone=True) * (2.0 if dtype == "bfloat16" else 1.0)
+
+
+# ----------------------------------------------------------------------------- the whole model, cut in every way
+
+
+@pytest.mark.parametrize("dtype", DTYPES)
+@pytest.mark.parametrize("name", ["mix", "wide", "tensor"])
+@pytest.mark.parametrize("family", ["whole", "tail", "portions", "mixed"])
+def test_cuts_equal_the_plain_implementation(fosepel_folders, name, family, dtype):
+    cases.replay(fosepel_folders(name), cases.prompts_for(name), family, DEV, dtype)
+
+
+@pytest.mark.parametrize("dtype", DTYPES)
+def test_portions_of_two_tokens_and_pages_of_64(fosepel_folders, dtype):
+    folder = fosepel_folders("mix")
+    cases.replay(folder, cases.prompts_for("mix")[1:4], "portions", DEV, dtype, sizes=(2,))
+    cases.replay(folder, cases.prompts_for("mix"), "mixed", DEV, dtype, page_size=64)
+    cases.replay(folder, cases.prompts_for("mix"), "tail", DEV, dtype, page_size=64, tail=40)
+    # five taps keep four inputs: portions of one to three tokens shift what is kept
+    cases.replay(fosepel_folders("wide"), cases.prompts_for("wide", lengths=[23, 9]), "portions", DEV, dtype, sizes=(2, 1, 3, 1, 1, 2))
+
+
+@pytest.mark.parametrize("dtype", DTYPES)
+def test_batches_of_unequal_requests_equal_each_alone_and_rows_are_used_again(fosepel_folders, dtype):
+    """Three requests of different lengths stepped together, one of them sitting a step out; then the same rows and
+    pages serve other requests.  In 32-bit the logits are those of each request alone, bit for bit."""
+    from vt_transformer_b200.engine.batch import StepEntry
+    folder = fosepel_folders("mix")
+    runner = cases.runner_for(folder, DEV, dtype, num_pages=16, max_requests=3)
+    for turn in range(2):
+        prompts = cases.prompts_for("mix", seed=turn, lengths=[50, 7, 23])
+        alone = []
+        for p in prompts:
+            row = runner.admit()
+            alone.append(cases.step_all(runner, row, p, [len(p)]))
+            runner.release(row)
+        rows = [runner.admit() for _ in prompts]
+        done, got = [0, 0, 0], [[], [], []]
+        step = 0
+        while any(d < len(p) for d, p in zip(done, prompts)):
+            entries, who = [], []
+            for i, p in enumerate(prompts):
+                if done[i] < len(p) and not (i == 1 and step == 1):
+                    k = min([9, 1, 4][(i + step) % 3], len(p) - done[i])
+                    entries.append(StepEntry(rows[i], p[done[i]:done[i] + k], list(range(k))))
+                    who.append((i, k))
+                    done[i] += k
+            logits, at = runner.step(entries).double().cpu(), 0
+            for i, k in who:
+                got[i].append(logits[at:at + k])
+                at += k
+            step += 1
+        runner.check_status()
+        for i, p in enumerate(prompts):
+            cases.within(torch.cat(got[i]), folder, p, dtype)
+            if dtype == "float32":
+                assert torch.equal(torch.cat(got[i]), alone[i]), "logits depend on what else is in the batch"
+        for r in rows:
+            runner.release(r)
+        runner.cache.check()
+
+
+# ----------------------------------------------------------------------------- far keys, page borders, the first tokens
+
+
+@pytest.mark.parametrize("dtype", DTYPES)
+@pytest.mark.parametrize("name", ["attention_alone", "parallel_alone", "parallel2_alone"])
+def test_a_key_hundreds_of_tokens_back_and_at_page_borders(fosepel_folders, tmp_path, name, dtype):
+    """Each attention alone, sharpened so that one key can carry a position's weight: a marked token at position 3, at a page's
+    last place and at the next page's first decides the logits near position 389, across 24 pages; whole, in portions, and
+    with the asking tokens decoded one by one."""
+    folder = cases.rewritten(fosepel_folders(name), str(tmp_path / "far"), lambda t: cases.sharpen_attention(t, 4.0))
+    base = cases.prompts_for(name, lengths=[392])[0]
+    plain_base = _logits(folder, base)
+    bound = cases.tol(dtype, plain_base, alone=True) * (2.0 if dtype == "bfloat16" else 1.0)
+    runner = cases.runner_for(folder, DEV, dtype, num_pages=26, max_requests=1)
+    for where in (3, 15, 16, 383):
+        best = (0.0, 0)
+        for tok in range(0, 128, 4):                    # the token that shows best at the asking positions
+            ids = list(base)
+            ids[where] = tok
+            d = (_logits(folder, ids)[384:] - plain_base[384:]).abs().max()
+            best = max(best, (float(d), tok))
+        assert best[0] > 3 * bound, (where, best)
+        ids = list(base)
+        ids[where] = best[1]
+        ref = _logits(folder, ids)
+        for cuts in ([len(ids)], [150, 37, 190] + [1] * 15, [380] + [1] * 12):
+            row = runner.admit()
+            got = cases.step_all(runner, row, ids, cuts)
+            runner.release(row)
+            assert float((got - ref).abs().max()) <= bound, (where, cuts)
+
+
+@pytest.mark.parametrize("dtype", DTYPES)
+@pytest.mark.parametrize("name", ["parallel_alone", "parallel2_alone"])
+def test_a_token_far_back_still_decides_a_recurrent_state(fosepel_folders, tmp_path, name, dtype):
+    """Decays and forget gates of nearly one: what token 2 wrote into the state decides the logits 400 tokens later.  The
+    prompt runs in portions, its end token by token; the plain logits with another token 2 differ far beyond the bound."""
+    def blind(t):                                       # the attention beside the recurrence sees nothing of it: its result is taken out
+        cases.remember_everything(t)
+        t["l0.mix.left.out"] = torch.zeros_like(t["l0.mix.left.out"])
+    folder = cases.rewritten(fosepel_folders(name), str(tmp_path / "long"), blind)
+    ids = cases.prompts_for(name, lengths=[420])[0]
+    other = list(ids)
+    other[2] = (ids[2] + 17) % 128
+    ref, ref_other = _logits(folder, ids), _logits(folder, other)
+    assert float((ref[-1] - ref_other[-1]).abs().max()) > 3 * cases.tol("bfloat16", ref, alone=True)
+    runner = cases.runner_for(folder, DEV, dtype, num_pages=27, max_requests=2)
+    for tokens, want in ((ids, ref), (other, ref_other)):
+        row = runner.admit()
+        got = cases.step_all(runner, row, tokens, [150, 37, 200] + [1] * 40)
+        runner.release(row)
+        assert float((got - want).abs().max()) <= cases.tol(dtype, want, alone=True)
+
+
+@pytest.mark.parametrize("dtype", DTYPES)
+def test_the_state_of_a_row_that_is_used_again_starts_from_zero(fosepel_folders, dtype):
+    """A request that leaves a row behind must not hand its state or its convolutions' last inputs to the next request in it."""
+    folder = fosepel_folders("parallel_alone")
+    a, b = cases.prompts_for("parallel_alone", lengths=[9, 6])
+    runner = cases.runner_for(folder, DEV, dtype, num_pages=2, max_requests=1)
+    for ids in (a, b, a):
+        row = runner.admit()
+        got = cases.step_all(runner, row, ids, [4, 1, 2])
+        runner.release(row)
+        ref = _logits(folder, ids)
+        assert float((got - ref).abs().max()) <= cases.tol(dtype, ref, alone=True)
+    ref = _logits(folder, [a[-1]] + b)                  # a stale input of the convolutions would show at the first token
+    assert float((ref[1] - _logits(folder, b)[0]).abs().max()) > 3 * cases.tol(dtype, ref, alone=True)
+
+
+@pytest.mark.parametrize("dtype", DTYPES)
+def test_first_tokens_and_long_decoding(fosepel_folders, dtype):
+    """A request of one token, then 150 tokens decoded one by one (through the captured graphs of single-token steps, over
+    page borders and over the steps of the query temperature), beside a second request that joins and leaves."""
+    from vt_transformer_b200.engine.batch import StepEntry
+    folder = fosepel_folders("mix")
+    a, b = cases.prompts_for("mix", seed=9, lengths=[151, 40])
+    runner = cases.runner_for(folder, DEV, dtype, num_pages=14, max_requests=2)
+    ra = runner.admit()
+    got_a, got_b, rb = [], [], None
+    for i, tok in enumerate(a):
+        entries = [StepEntry(ra, [tok], [0])]
+        if 30 <= i < 30 + len(b):
+            if rb is None:
+                rb = runner.admit()
+            entries.append(StepEntry(rb, [b[i - 30]], [0]))
+        logits = runner.step(entries).double().cpu()
+        got_a.append(logits[0])
+        if len(entries) == 2:
+            got_b.append(logits[1])
+            if i - 30 == len(b) - 1:
+                runner.release(rb)
+    runner.check_status()
+    for got, ids in ((got_a, a), (got_b, b)):
+        cases.within(torch.stack(got), folder, ids, dtype)
+    assert runner._graphs, "single-token steps did not run as captured graphs"
+
+
+# ----------------------------------------------------------------------------- the entry point
+
+
+@pytest.mark.parametrize("dtype", DTYPES)
+@pytest.mark.parametrize("name", ["mix", "wide"])
+def test_greedy_generation_through_the_entry_point(fosepel_folders, name, dtype):
+    cases.greedy_generation(fosepel_folders(name), name, DEV, dtype)
+
+
+def test_trace_replay_command(fosepel_folders, tmp_path):
+    folder = fosepel_folders("mix")
+    prompts = cases.prompts_for("mix")
+    trace = helpers.trace_mixed(prompts, max_live=4, seed=2)
+    got = helpers.run_trace_cli(folder, trace, "float32", str(tmp_path / "out"), helpers.tokens_needed(trace, 64))
+    cases.compare(folder, prompts, trace, got, "float32")

@@ -212,7 +212,7 @@ def test_a_part_may_bring_an_initialiser_of_its_own():
     from vt_transformer_b200.parts import ParamSpec
     from vt_transformer_b200.weights import random_tensor, register_initialiser, unregister_initialiser
     spec = ParamSpec((4, 6), init="toy_ramp")
-    with pytest.raises(ValueError, match="unknown initialiser 'toy_ramp'.*known: normal, one_plus_normal, polynorm_coefficients, unit_uniform, zeros"):
+    with pytest.raises(ValueError, match="unknown initialiser 'toy_ramp'.*known: conv_taps, normal, one_plus_normal, polynorm_coefficients, unit_uniform, zeros"):
         random_tensor("x", spec, 0, 0.02)
     register_initialiser("toy_ramp", lambda shape, g, sigma, device: torch.arange(shape[0] * shape[1], dtype=torch.float32).view(shape) * sigma)
     try:

@@ -219,6 +219,20 @@ class Lightning(_Recurrent):
                            token_seq=ctx.token_seq)
 
 
+def _conv_taps(shape, g, sigma, device):
+    """The taps of a short convolution in the random-weights mode: of the order of a half whatever sigma is, so that every
+    tap counts."""
+    return torch.randn(shape, generator=g, dtype=torch.float32, device=device) * 0.4
+
+
+def _register_conv_taps():
+    from ..weights.loader import register_initialiser
+    register_initialiser("conv_taps", _conv_taps, replace=True)
+
+
+_register_conv_taps()
+
+
 @register_part("mixer", "gated_delta")
 class GatedDelta(_Recurrent):
     """See ``GatedDeltaSpec``.  Projections q, k, v, gate and the two matrices of beta and of the decay are one product; the

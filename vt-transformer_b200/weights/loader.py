@@ -179,8 +179,6 @@ _INITIALISERS = {
     "zeros": lambda shape, g, sigma, device: torch.zeros(shape, dtype=torch.float32, device=device),
     # numbers between 0 and 1 (how much of the token before a token shift mixes in)
     "unit_uniform": lambda shape, g, sigma, device: torch.rand(shape, generator=g, dtype=torch.float32, device=device),
-    # the taps of a short convolution over time: of the order of a half whatever sigma is, so that every tap counts
-    "conv_taps": lambda shape, g, sigma, device: torch.randn(shape, generator=g, dtype=torch.float32, device=device) * 0.4,
     # the four numbers of a PolyNorm activation: three weights of the order of a half that differ, and a small offset
     "polynorm_coefficients": lambda shape, g, sigma, device: torch.tensor([0.8, 0.6, 0.3, 0.1], dtype=torch.float32, device=device)
     + torch.randn(shape, generator=g, dtype=torch.float32, device=device) * sigma,
