@@ -422,6 +422,29 @@ def _geponex_config(width, ff, lig, att, pairs=2):
             "postln_alpha": 2.0}
 
 
+def _fosepel_config(width, ff, mem, att, delta):
+    """A layer of each kind and a second attention layer, each with a dense feed-forward of ``ff``: a softmax attention with
+    capped scores, a query temperature and learned sinks beside a matrix memory (``mem``: heads, keys' and values' sizes); a
+    softmax attention with half of each head rotated (ramped frequencies) and an element-wise gate; a softmax attention with
+    a sink of score 0 and a gate a head beside the delta rule with one decay a head (``delta``: heads, head size; half as
+    many heads of q and k, values twice as wide, convolutions of 4 taps).  ``att``: (heads, kv heads, head size) of the Qwen2
+    model of equal size."""
+    heads, kv_heads, dim = att
+    left = {"heads": heads, "kv_heads": kv_heads, "dim": dim, "vdim": dim, "scale": dim ** -0.5}
+    rotary = {"type": "attention", "mlp": {"kind": "dense", "ff": ff}, "mixer": dict(left, rot={
+        "dims": dim // 2, "base": 1e6, "scaling": {"factor": 8.0, "original": 8192, "fast": 32.0, "slow": 1.0}})}
+    layers = [
+        {"type": "parallel_2", "mlp": {"kind": "dense", "ff": ff}, "mixer": {
+            "left": dict(left, softcap=50.0, q_temp={"coef": 0.1, "every": 1024}),
+            "right": {"heads": mem[0], "dim": mem[1], "vdim": mem[2], "gate_cap": 15.0}}},
+        rotary,
+        {"type": "parallel", "mlp": {"kind": "dense", "ff": ff}, "mixer": {
+            "left": dict(left), "right": {"heads": delta[0], "kv_heads": max(1, delta[0] // 2), "dim": delta[1], "vdim": 2 * delta[1], "conv": 4}}},
+        rotary,
+    ]
+    return {"architecture": "Fosepel", "vocab": 32768, "width": width, "layers": layers, "norm": {"eps": 1e-6}, "logit_softcap": 30.0}
+
+
 DESIGN_SIZES = {
     # name: width, feed-forward, (gla heads, dim, vdim), (attention heads, kv heads, head size), (delta heads, dim), chunk
     "w1024": (1024, 4096, (8, 64, 128), (16, 2, 64), (8, 64), 1024),
@@ -433,6 +456,8 @@ DESIGNS = {
     # (the recurrent layer has the gated linear attention's sizes; the window is the other design's chunk)
     "vegilix": lambda width, ff, gla, att, delta, chunk: _vegilix_config(width, ff, gla, att, chunk),
     "geponex": lambda width, ff, gla, att, delta, chunk: _geponex_config(width, ff, gla, att),
+    # (the matrix memory has the gated linear attention's sizes)
+    "fosepel": lambda width, ff, gla, att, delta, chunk: _fosepel_config(width, ff, gla, att, delta),
 }
 
 
@@ -469,7 +494,7 @@ def design_points(design: str, sizes, steps: int, warmup: int) -> int:
     def per_kernel(runner, entries):
         """Device time of each of the package's kernels in one eager step, by the name of the op."""
         names = [n for n in ("embedding", "rmsnorm", "layernorm", "polynorm", "head_norm_gate", "gla_scan", "delta_scan",
-                             "retention_scan", "route_experts", "route_topk", "token_shift", "latent_prepare", "head_matmul", "attention_latent", "xielu",
+                             "retention_scan", "gated_delta_scan", "conv_tail_update", "memory_scan", "normed_sum", "add_rows", "route_experts", "route_topk", "token_shift", "latent_prepare", "head_matmul", "attention_latent", "xielu",
                              "gate_clamp", "attention_differential", "attention_prepare", "attention_general", "rope_store", "paged_attention", "rope_attention", "linear",
                              "linear_silu_mul", "linear_to_stream", "logits_scale_cap") if hasattr(ops, n)]
         saved, events = {n: getattr(ops, n) for n in names}, []

@@ -613,3 +613,12 @@ def normed_sum(parts, weights, eps, scales, out):
 
 def add_rows(x, other):
     x.add_(other)
+
+
+def gate_into(src, y, gate_col, mode, dst, dst_col, scale, heads, v_dim):
+    v = src.float().view(src.shape[0], heads, v_dim) * scale
+    if mode == 1:
+        v = v * torch.sigmoid(y[:, gate_col:gate_col + heads].float())[:, :, None]
+    elif mode == 2:
+        v = v * torch.sigmoid(y[:, gate_col:gate_col + heads * v_dim].float()).view(-1, heads, v_dim)
+    dst[:, dst_col:dst_col + heads * v_dim] = v.reshape(src.shape[0], -1).to(dst.dtype)

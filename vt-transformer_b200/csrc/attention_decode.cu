@@ -23,6 +23,9 @@ cudaError_t launch_attention_decode(const void* qkv, int qkv_stride, void* out, 
     const bool with_scratch = part_o != nullptr && part_ml != nullptr && counters != nullptr;
     const bool cluster = n_splits > 1 && n_splits <= 8 && !with_scratch;
     AttnParams p;
+    p.sinks = nullptr;
+    p.softcap = 0.f;
+    p.scale = scale;
     p.cluster_merge = cluster ? 1 : 0;
     p.qkv = (const __nv_bfloat16*)qkv;
     p.qkv_stride = qkv_stride;

@@ -92,6 +92,17 @@ attention_mma_kernel(const AttnParams p) {
 #pragma unroll
     for (int i = 0; i < D / 8; ++i) o[i][0] = o[i][1] = o[i][2] = o[i][3] = 0.f;
     float mrow[2] = {-INFINITY, -INFINITY}, lrow[2] = {0.f, 0.f};
+    if (p.sinks != nullptr && split == 0) {
+        // the sink is a first key without a value: its score is the running maximum to begin with and it counts once in the
+        // sum (the four threads of a row add their sums at the end, so one of them holds it)
+#pragma unroll
+        for (int i = 0; i < 2; ++i) {
+            if (!valid[i]) continue;
+            mrow[i] = p.sinks[head[i]] * 1.4426950408889634f;
+            lrow[i] = tq == 0 ? 1.f : 0.f;
+        }
+    }
+    const float cap = p.softcap, cap_log2 = p.softcap * 1.4426950408889634f, over_cap = p.softcap > 0.f ? p.scale / p.softcap : 0.f;
 
     const int* table = p.block_table + (size_t)seq * p.table_stride;
     auto load_block = [&](int blk, int stage) {
@@ -168,7 +179,7 @@ attention_mma_kernel(const AttnParams p) {
             for (int j = 0; j < KB / 8; ++j) {
 #pragma unroll
                 for (int e = 0; e < 4; ++e) {
-                    s[j][e] *= p.scale_log2;
+                    s[j][e] = cap > 0.f ? cap_log2 * tanhf(s[j][e] * over_cap) : s[j][e] * p.scale_log2;
                     mnew[e >> 1] = fmaxf(mnew[e >> 1], s[j][e]);
                 }
             }
@@ -180,7 +191,7 @@ attention_mma_kernel(const AttnParams p) {
                     const int i = e >> 1;
                     const int key = kb + j * 8 + 2 * tq + (e & 1);
                     const bool see = valid[i] && key <= pos[i] && key >= first_visible_key(pos[i], p.window, p.chunk);
-                    s[j][e] = see ? s[j][e] * p.scale_log2 : -INFINITY;
+                    s[j][e] = see ? (cap > 0.f ? cap_log2 * tanhf(s[j][e] * over_cap) : s[j][e] * p.scale_log2) : -INFINITY;
                     mnew[i] = fmaxf(mnew[i], s[j][e]);
                 }
             }
@@ -342,7 +353,8 @@ cudaError_t launch_attention_mma(const void* qkv, int qkv_stride, void* out, con
                                  const int* cu_q, const int* q_start, const int* block_table, int table_stride,
                                  const int* tiles, int n_tiles, int n_pages, int n_tokens, int heads, int kv_heads,
                                  int head_dim, int page_size, int window, float scale, int warps, int n_splits,
-                                 float* part_o, float* part_ml, int* status, cudaStream_t stream, int chunk) {
+                                 float* part_o, float* part_ml, int* status, cudaStream_t stream, int chunk, const float* sinks,
+                                 float softcap) {
     if (n_tiles == 0 || n_tokens == 0) return cudaSuccess;
     if (!attention_mma_supports(head_dim, heads, kv_heads, warps) || page_size % 16 != 0) return cudaErrorInvalidValue;
     if (n_splits > 1 && (part_o == nullptr || part_ml == nullptr)) return cudaErrorInvalidValue;
@@ -373,6 +385,9 @@ cudaError_t launch_attention_mma(const void* qkv, int qkv_stride, void* out, con
     p.window = window;
     p.chunk = chunk;
     p.scale_log2 = scale * 1.4426950408889634f;
+    p.scale = scale;
+    p.sinks = sinks;
+    p.softcap = softcap;
     p.tokens_per_tile = (16 * warps) / (heads / kv_heads);
     p.n_splits = n_splits < 1 ? 1 : n_splits;
     p.run_blocks = 0;

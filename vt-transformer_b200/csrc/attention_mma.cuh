@@ -46,6 +46,11 @@ struct AttnParams {
     // the product before them left (its inner dimension cut over CTAs): they are added, in order, where they are read
     const float* qkv_shares;
     int n_shares;
+    // prompt portions (attention_mma.cu): one more term exp(sinks[head]) in the softmax's denominator, without a key or a
+    // value and not scaled (null: none); a score becomes softcap * tanh(score / softcap) after the scale (0: no cap)
+    const float* sinks;
+    float softcap;
+    float scale;            // the scale as it is (scale_log2 without the logarithm's factor)
 };
 
 namespace {

@@ -187,6 +187,20 @@ void scale_into(const Tensor& src, Tensor& dst, int64_t dst_col, double scale) {
                                         dst_col, (float)scale, stream_of(src)), "scale_into");
 }
 
+void gate_into(const Tensor& src, const Tensor& y, int64_t gate_col, int64_t mode, Tensor& dst, int64_t dst_col, double scale, int64_t heads,
+               int64_t v_dim) {
+    check_cuda(src, "src"); check_cuda(y, "y"); check_cuda(dst, "dst");
+    TORCH_CHECK(src.dim() == 2 && dst.dim() == 2 && y.dim() == 2 && src.size(0) == dst.size(0) && y.size(0) == src.size(0) &&
+                src.scalar_type() == dst.scalar_type() && y.scalar_type() == src.scalar_type() && src.size(1) == heads * v_dim,
+                "gate_into: src [tokens, heads * v_dim], y and dst with as many rows, of one dtype");
+    TORCH_CHECK(mode >= 0 && mode <= 2, "gate_into: mode 0, 1 or 2");
+    check_cols(dst, dst_col, src.size(1), "gate_into");
+    if (mode != 0) check_cols(y, gate_col, mode == 1 ? heads : heads * v_dim, "gate_into (gate)");
+    c10::cuda::CUDAGuard guard(src.device());
+    check_launch(vtb::launch_gate_into(dtype_code(src, "src"), src.data_ptr(), y.data_ptr(), y.size(1), gate_col, mode, dst.data_ptr(), src.size(0),
+                                       heads, v_dim, dst.size(1), dst_col, (float)scale, stream_of(src)), "gate_into");
+}
+
 void check_scan(const Tensor& y, const Tensor& state, const Tensor& cu_q, const Tensor& rows, const Tensor& o, int64_t heads, int64_t dim,
                 int64_t v_dim, const char* who) {
     check_cuda(y, "y"); check_f32(state, "state"); check_i32(cu_q, "cu_q"); check_i32(rows, "rows"); check_f32(o, "o");
@@ -971,11 +985,19 @@ bool attention_mma_supports(int64_t head_dim, int64_t heads, int64_t kv_heads, i
 void attention_mma(const Tensor& qkv, Tensor& out, const Tensor& k_cache, const Tensor& v_cache, const Tensor& cu_q,
                    const Tensor& q_start, const Tensor& block_table, c10::optional<Tensor> tiles, int64_t heads,
                    int64_t kv_heads, int64_t head_dim, int64_t window, double scale, int64_t warps, int64_t n_splits,
-                   c10::optional<Tensor> part_o, c10::optional<Tensor> part_ml, c10::optional<Tensor> status, int64_t chunk) {
+                   c10::optional<Tensor> part_o, c10::optional<Tensor> part_ml, c10::optional<Tensor> status, int64_t chunk,
+                   c10::optional<Tensor> sinks, double softcap) {
     check_cuda(qkv, "qkv"); check_cuda(out, "out"); check_i32(cu_q, "cu_q"); check_i32(q_start, "q_start");
     check_i32(block_table, "block_table");
     TORCH_CHECK(qkv.scalar_type() == torch::kBFloat16 && out.scalar_type() == torch::kBFloat16,
                 "attention_mma: bfloat16 only");
+    const float* sp = nullptr;
+    if (sinks.has_value()) {
+        check_f32(*sinks, "sinks");
+        TORCH_CHECK(sinks->numel() == heads, "attention_mma: one sink a head");
+        sp = sinks->data_ptr<float>();
+    }
+    TORCH_CHECK(softcap >= 0.0, "attention_mma: softcap not negative");
     TORCH_CHECK(qkv.dim() == 2 && qkv.size(1) >= heads * head_dim, "attention_mma: qkv must hold the queries first");
     TORCH_CHECK(out.dim() == 2 && out.size(0) == qkv.size(0) && out.size(1) == heads * head_dim,
                 "attention_mma: out must be [tokens, heads * head_dim]");
@@ -1011,7 +1033,8 @@ void attention_mma(const Tensor& qkv, Tensor& out, const Tensor& k_cache, const 
                                            v_cache.data_ptr(), cu_q.data_ptr<int>(), q_start.data_ptr<int>(),
                                            block_table.data_ptr<int>(), block_table.size(1), tp, n_tiles,
                                            k_cache.size(0), n_tokens, heads, kv_heads, head_dim, k_cache.size(2), window,
-                                           (float)scale, warps, n_splits, po, pm, status_ptr(status), stream_of(qkv), (int)chunk),
+                                           (float)scale, warps, n_splits, po, pm, status_ptr(status), stream_of(qkv), (int)chunk, sp,
+                                           (float)softcap),
                  "attention_mma");
 }
 
@@ -1200,6 +1223,7 @@ PYBIND11_MODULE(TORCH_EXTENSION_NAME, m) {
           py::arg("status") = py::none(), py::arg("keep_first") = 0, py::arg("maps") = 1, py::arg("lam") = 0.0, py::arg("sub_eps") = 0.0,
           py::arg("sinks") = py::none(), py::arg("values_in_keys") = false, py::arg("softcap") = 0.0, py::arg("gate_mode") = 0,
           py::arg("gate_col") = 0);
+    m.def("gate_into", &gate_into);
     m.def("gated_delta_scan", &gated_delta_scan);
     m.def("conv_tail_update", &conv_tail_update);
     m.def("memory_scan", &memory_scan);
@@ -1257,7 +1281,7 @@ PYBIND11_MODULE(TORCH_EXTENSION_NAME, m) {
           py::arg("cu_q"), py::arg("q_start"), py::arg("block_table"), py::arg("tiles"), py::arg("heads"),
           py::arg("kv_heads"), py::arg("head_dim"), py::arg("window"), py::arg("scale"), py::arg("warps"),
           py::arg("n_splits"), py::arg("part_o") = py::none(), py::arg("part_ml") = py::none(),
-          py::arg("status") = py::none(), py::arg("chunk") = 0);
+          py::arg("status") = py::none(), py::arg("chunk") = 0, py::arg("sinks") = py::none(), py::arg("softcap") = 0.0);
     m.def("attention_tc_supports", &attention_tc_supports);
     m.def("attention_tc", &attention_tc, py::arg("qkv"), py::arg("out"), py::arg("k_cache"), py::arg("v_cache"),
           py::arg("cu_q"), py::arg("q_start"), py::arg("block_table"), py::arg("tiles"), py::arg("heads"),

@@ -376,6 +376,33 @@ cudaError_t launch_scale_into(int dtype, const void* src, void* dst, int n_token
     return launch(scale_into_kernel<float>, blocks, 256, 0, stream, (const float*)src, (float*)dst, total, n, dst_stride, dst_col, scale);
 }
 
+template <typename T>
+__global__ void gate_into_kernel(const T* __restrict__ src, const T* __restrict__ y, int y_stride, int gate_col, int mode,
+                                 T* __restrict__ dst, long long total, int heads, int v_dim, int dst_stride, int dst_col, float scale) {
+    pdl_launch();
+    pdl_wait();
+    const int n = heads * v_dim;
+    for (long long e = (long long)blockIdx.x * blockDim.x + threadIdx.x; e < total; e += (long long)gridDim.x * blockDim.x) {
+        const long long t = e / n;
+        const int i = (int)(e % n);
+        float v = to_float(src[e]) * scale;
+        if (mode != 0) v *= 1.f / (1.f + expf(-to_float(y[t * y_stride + gate_col + (mode == 1 ? i / v_dim : i)])));
+        dst[t * dst_stride + dst_col + i] = from_float<T>(v);
+    }
+}
+
+cudaError_t launch_gate_into(int dtype, const void* src, const void* y, int y_stride, int gate_col, int mode, void* dst, int n_tokens,
+                             int heads, int v_dim, int dst_stride, int dst_col, float scale, cudaStream_t stream) {
+    const long long total = (long long)n_tokens * heads * v_dim;
+    if (total == 0) return cudaSuccess;
+    const int blocks = (int)min((total + 255) / 256, (long long)148 * 16);
+    if (dtype == kBF16)
+        return launch(gate_into_kernel<__nv_bfloat16>, blocks, 256, 0, stream, (const __nv_bfloat16*)src, (const __nv_bfloat16*)y, y_stride,
+                      gate_col, mode, (__nv_bfloat16*)dst, total, heads, v_dim, dst_stride, dst_col, scale);
+    return launch(gate_into_kernel<float>, blocks, 256, 0, stream, (const float*)src, (const float*)y, y_stride, gate_col, mode, (float*)dst,
+                  total, heads, v_dim, dst_stride, dst_col, scale);
+}
+
 // ------------------------------------------------------------------------- silu * up
 
 template <typename T>

@@ -205,6 +205,10 @@ cudaError_t launch_gate_clamp(int dtype, const void* gu, void* out, int n_tokens
                               int split, float limit2, cudaStream_t stream);
 
 // dst[t, dst_col + i] = scale * src[t, i] for src [n_tokens, n] and dst [n_tokens, dst_stride], the product in 32-bit.
+// dst[t, dst_col + h v_dim + i] = scale * src[t, h v_dim + i] * sigmoid(y[t, gate_col + (mode 1: h; mode 2: h v_dim + i)]);
+// mode 0: no gate (scale_into).
+cudaError_t launch_gate_into(int dtype, const void* src, const void* y, int y_stride, int gate_col, int mode, void* dst, int n_tokens,
+                             int heads, int v_dim, int dst_stride, int dst_col, float scale, cudaStream_t stream);
 cudaError_t launch_scale_into(int dtype, const void* src, void* dst, int n_tokens, int n, int dst_stride, int dst_col, float scale,
                               cudaStream_t stream);
 
@@ -281,7 +285,7 @@ cudaError_t launch_attention_mma(const void* qkv, int qkv_stride, void* out, con
                                  const int* cu_q, const int* q_start, const int* block_table, int table_stride,
                                  const int* tiles, int n_tiles, int n_pages, int n_tokens, int heads, int kv_heads,
                                  int head_dim, int page_size, int window, float scale, int warps, int n_splits,
-                                 float* part_o, float* part_ml, int* status, cudaStream_t stream, int chunk = 0);
+                                 float* part_o, float* part_ml, int* status, cudaStream_t stream, int chunk = 0, const float* sinks = nullptr, float softcap = 0.f);
 
 // Attention of prompt portions on tcgen05 tensor cores with the scores in tensor memory (head size 128):
 // tiles of 128 rows of (token, head of the group) as in launch_attention_mma with 8 warps.

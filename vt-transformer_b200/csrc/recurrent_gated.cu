@@ -7,7 +7,7 @@
 //   matrix memory  m' = max(f_t + m, i_t);  S <- exp(f_t + m - m') S + exp(i_t - m') k_t v_t^T;  n likewise with k_t alone;
 //                  o_t = S^T q_t / (max(|n . q_t|, exp(-m')) + eps)
 // Column j of S depends on column j alone: a warp owns 32 columns of one (sequence, head), a thread keeps KD rows of its
-// column in registers, and G threads share a column where dim > KD (their partial sums meet in shared memory, in the
+// column in registers (16), and G = dim / 16 threads share a column (their partial sums meet in shared memory, in the
 // order of g).  The step's tokens of the sequence are staged 16 at a time: the convolutions and their silu, the unit
 // vectors, the gates, the running maximum and the normalizer are formed once for all columns, in 32-bit; then the
 // warps walk the batch out of shared memory.  A decoded token is a walk of one token.  The order of every sum depends
@@ -22,8 +22,11 @@ namespace {
 
 constexpr int kCols = 32;        // columns of the state a warp owns
 constexpr int kTokens = 16;      // tokens staged at once
-// Most threads of a CTA, by the rows a thread keeps in registers (64 rows want 255 registers a thread).
-constexpr int gated_threads(int kd) { return kd > 32 ? 256 : 512; }
+constexpr int kRows = 16;        // rows of its column that a thread keeps in registers
+constexpr int kMaxThreads = 1024;
+// Threads of a CTA in a step that is a long walk of few sequences: a head's column blocks then spread over several SMs
+// (each forms the gates again); steps of single tokens keep as many of a head's columns in one CTA as fit.
+constexpr int kWalkThreads = 256;
 
 struct GatedArgs {
     const void* y;               // [tokens, stride]: the projections
@@ -57,8 +60,9 @@ __device__ __forceinline__ float log_sigmoid_f(float z) { return z < 0.f ? z - l
 
 // MODE 0: the delta rule; 1: the matrix memory.  Block (32, G, CB): thread (c, g, cb) keeps rows [g KD, (g + 1) KD) of column
 // blockIdx.z * CB * 32 + cb * 32 + c.
-template <typename T, int KD, int MODE>
-__global__ void __launch_bounds__(gated_threads(KD))
+// WALK: the variant for long walks of few sequences, compiled for CTAs of 256 threads (and the registers they may have).
+template <typename T, int KD, int MODE, bool WALK>
+__global__ void __launch_bounds__(WALK ? kWalkThreads : kMaxThreads)
 gated_scan_kernel(const GatedArgs a) {
     extern __shared__ __align__(16) float smem[];
     pdl_launch();
@@ -332,12 +336,11 @@ template <typename T, int KD, int MODE>
 cudaError_t launch_gated_kd(const GatedArgs& a, int n_seqs, int most_threads, cudaStream_t stream) {
     GatedArgs args = a;
     const int G = (a.dim + KD - 1) / KD;
-    const int limit = most_threads > 0 ? min(most_threads, gated_threads(KD)) : gated_threads(KD);
+    const int limit = most_threads > 0 ? max(kCols * G, min(most_threads, kMaxThreads)) : kMaxThreads;
     // the matrix memory's normalizer wants a thread for every row of the head: at least dim_p threads
     int cb = max(1, min((a.v_dim + kCols - 1) / kCols, limit / (kCols * G)));
     cb = min(cb, 15);                                       // the groups' barriers are numbered 1 to 15
-    while (MODE == 1 && cb * kCols * G < G * KD) ++cb;
-    if (cb > 15 || cb * kCols * G > gated_threads(KD)) return cudaErrorInvalidValue;
+    if (cb > 15 || cb * kCols * G > kMaxThreads) return cudaErrorInvalidValue;
     args.groups = G;
     args.col_blocks = cb;
     const int dim_p = G * KD, cols = cb * kCols, per = 2 * dim_p + cols;
@@ -346,9 +349,10 @@ cudaError_t launch_gated_kd(const GatedArgs& a, int n_seqs, int most_threads, cu
     floats += MODE == 0 ? (size_t)(kTokens + taps - 1) * per + (size_t)taps * per : (size_t)kTokens * dim_p + 4;
     const size_t bytes = floats * sizeof(float);
     if (bytes > 200 * 1024) return cudaErrorInvalidValue;
-    auto kernel = gated_scan_kernel<T, KD, MODE>;
-    static std::atomic<unsigned long long> done{0};
-    if (cudaError_t e = allow_dynamic_smem(kernel, 200 * 1024, done); e != cudaSuccess) return e;
+    const bool walk = most_threads > 0 && cb * kCols * G <= kWalkThreads;
+    auto kernel = walk ? gated_scan_kernel<T, KD, MODE, true> : gated_scan_kernel<T, KD, MODE, false>;
+    static std::atomic<unsigned long long> done[2] = {{0}, {0}};
+    if (cudaError_t e = allow_dynamic_smem(kernel, 200 * 1024, done[walk ? 1 : 0]); e != cudaSuccess) return e;
     const dim3 grid(n_seqs, a.heads, (a.v_dim + cols - 1) / cols), block(kCols, G, cb);
     if (MODE == 1) {
         if (grid.z > 1) {
@@ -364,10 +368,9 @@ cudaError_t launch_gated_kd(const GatedArgs& a, int n_seqs, int most_threads, cu
 
 template <typename T, int MODE>
 cudaError_t launch_gated_t(const GatedArgs& a, int n_seqs, int most_threads, cudaStream_t stream) {
-    // a thread keeps the whole column where the head is small (no meeting inside a token); beyond 64 rows, 64 rows a thread
-    if (a.dim <= 16) return launch_gated_kd<T, 16, MODE>(a, n_seqs, most_threads, stream);
-    if (a.dim <= 32) return launch_gated_kd<T, 32, MODE>(a, n_seqs, most_threads, stream);
-    return launch_gated_kd<T, 64, MODE>(a, n_seqs, most_threads, stream);
+    // 16 rows a thread: the G = dim / 16 warps of a column block work side by side and meet only where the recurrence needs
+    // the whole column (the delta rule's S^T k, once a token)
+    return launch_gated_kd<T, kRows, MODE>(a, n_seqs, most_threads > 0 ? kWalkThreads : 0, stream);
 }
 
 }  // namespace

@@ -777,8 +777,24 @@ def rope_attention(qkv, out, cos_sin, k_cache, v_cache, ctx, block_table, heads:
 FUSE_ROPE = True    # False: always the separate rotation kernel (tests compare the two)
 
 
+def gate_into(src: torch.Tensor, y: torch.Tensor, gate_col: int, gate: str, dst: torch.Tensor, dst_col: int, scale: float, heads: int,
+              v_dim: int) -> torch.Tensor:
+    """dst[:, dst_col + h * v_dim + i] = scale * src[:, h * v_dim + i] * sigmoid(g) with g = y[:, gate_col + h] (``gate`` "head")
+    or y[:, gate_col + h * v_dim + i] ("element"); "none": the scale alone.  32-bit, one rounding."""
+    backend().gate_into(src, y, int(gate_col), _ATTENTION_GATES[gate], dst, int(dst_col), float(scale), int(heads), int(v_dim))
+    return dst
+
+
+def tensor_core_attention_takes_extras(dtype, heads: int, kv_heads: int, head_dim: int, v_dim: int, page_size: int) -> bool:
+    """Whether ``paged_attention`` takes ``sinks`` and ``softcap`` at these sizes (the mma.sync kernel's)."""
+    return (dtype == torch.bfloat16 and v_dim == head_dim and page_size % 16 == 0 and ATTENTION_KERNEL in ("auto", "mma")
+            and backend().attention_mma_supports(head_dim, heads, kv_heads, 1)
+            and backend().attention_mma_supports(head_dim, heads, kv_heads, 4))
+
+
 def paged_attention(qkv, out, k_cache, v_cache, ctx, block_table, heads: int, kv_heads: int, head_dim: int,
-                    window: Optional[int], scale: float, status=None, chunk: Optional[int] = None) -> torch.Tensor:
+                    window: Optional[int], scale: float, status=None, chunk: Optional[int] = None, sinks=None,
+                    softcap=None) -> torch.Tensor:
     """Attention of the step's tokens over the paged keys and values of their sequences.
     ``ctx`` is the step's ``StepContext``.  bfloat16 runs on the tensor cores where the kernel
     takes the sizes (head_dim a multiple of 16 up to 128; tcgen05 for prompt portions at 64 and 128): single-token steps with the keys of a
@@ -790,6 +806,21 @@ def paged_attention(qkv, out, k_cache, v_cache, ctx, block_table, heads: int, kv
     w = int(window) if window else 0
     c = int(chunk) if chunk else 0
     group = heads // kv_heads
+    if sinks is not None or softcap:
+        # ``sinks`` [heads] float32: one more term exp(sinks[h]) in the denominator; ``softcap`` c: a score becomes
+        # c tanh(score / c).  The mma.sync kernel takes both: tiles of (token, head of the group) rows for portions, a tile a
+        # sequence in steps of single tokens.
+        if not tensor_core_attention_takes_extras(qkv.dtype, heads, kv_heads, head_dim, head_dim, k_cache.shape[2]):
+            raise ValueError("paged_attention: sinks and capped scores run on the tensor cores in bfloat16 at head sizes that are "
+                             "multiples of 16 up to 128; ops.attention_general takes the others")
+        if ctx.max_q_len == 1:
+            warps, tiles = 1, None
+        else:
+            warps = 8 if ctx.max_q_len * group >= 128 and be.attention_mma_supports(head_dim, heads, kv_heads, 8) else 4
+            tiles = _attention_tiles(ctx, (16 * warps) // group, qkv.device)
+        be.attention_mma(qkv, out, k_cache, v_cache, ctx.cu_q, ctx.q_start, block_table, tiles, heads, kv_heads, head_dim, w,
+                         float(scale), warps, 1, None, None, status, chunk=c, sinks=sinks, softcap=float(softcap) if softcap else 0.0)
+        return out
     if qkv.dtype == torch.bfloat16 and ATTENTION_KERNEL in ("auto", "mma"):
         if ctx.max_q_len == 1 and be.attention_mma_supports(head_dim, heads, kv_heads, 1):
             span = _key_span(ctx.max_kv_len, w, c)
@@ -968,6 +999,6 @@ def _counted(fn):
     return wrapper
 
 
-for _name in ("gated_delta_scan", "conv_tail_update", "memory_scan", "normed_sum", "add_rows", "embedding", "logits_scale_cap", "rmsnorm", "layernorm", "polynorm", "scale_into", "head_norm_gate", "gla_scan", "delta_scan", "retention_scan", "route_experts", "attention_differential", "route_topk", "expert_lists", "gather_picks", "combine_picks",
+for _name in ("gate_into", "gated_delta_scan", "conv_tail_update", "memory_scan", "normed_sum", "add_rows", "embedding", "logits_scale_cap", "rmsnorm", "layernorm", "polynorm", "scale_into", "head_norm_gate", "gla_scan", "delta_scan", "retention_scan", "route_experts", "attention_differential", "route_topk", "expert_lists", "gather_picks", "combine_picks",
               "token_shift", "latent_prepare", "head_matmul", "attention_latent", "xielu", "gate_clamp", "attention_prepare", "attention_general", "silu_mul", "rope_store", "linear", "paged_attention", "argmax", "sample"):  # the others count where they launch
     globals()[_name] = _counted(globals()[_name])

@@ -207,18 +207,22 @@ class GeneralAttention(ProjectedMixer):
                               cache.block_table, s.heads, s.kv_heads, s.head_dim, self.v_dim, store=cache.writes, status=ctx.status,
                               q_weight=self.q_weight, k_weight=self.k_weight, norm_first=whole, whole_projection=whole,
                               rot_mult=getattr(self.position, "mult", 1.0), q_temp=s.q_temp)
-        extras = s.softcap is not None or self.sinks is not None or s.gate != "none"
-        if (not extras and cols[0] == 0 and not s.keep_first
-                and ops.tensor_core_attention_takes(y.dtype, s.heads, s.kv_heads, s.head_dim, self.v_dim, cache.page_size)):
+        gated = s.gate != "none"
+        extras = s.softcap is not None or self.sinks is not None
+        takes = ops.tensor_core_attention_takes_extras if extras else ops.tensor_core_attention_takes
+        if cols[0] == 0 and not s.keep_first and takes(y.dtype, s.heads, s.kv_heads, s.head_dim, self.v_dim, cache.page_size):
             # values as wide as keys at a head size the tensor-core kernels take: the kernels of the plain attention walk
-            # the keys (tcgen05 for long portions, mma.sync tiles, the single-token kernel), with the chunks as one more
-            # bound of the keys a row sees.  They write a tensor of their own, which is then scaled into its columns.
+            # the keys (tcgen05 for long portions, mma.sync tiles, the single-token kernel; the mma.sync kernel where there
+            # is a sink or a cap), with the chunks as one more bound of the keys a row sees.  They write a tensor of their
+            # own, which is then gated and scaled into its columns.
             n = s.heads * self.v_dim
-            direct = out_col == 0 and out.shape[1] == n and out_scale == 1.0
+            direct = out_col == 0 and out.shape[1] == n and out_scale == 1.0 and not gated
             o = out if direct else torch.empty((y.shape[0], n), dtype=y.dtype, device=y.device)
             ops.paged_attention(y, o, k_pages, v_pages, ctx, cache.block_table, s.heads, s.kv_heads, s.head_dim, s.window,
-                                self.scale, status=ctx.status, chunk=s.chunk)
-            if not direct:
+                                self.scale, status=ctx.status, chunk=s.chunk, sinks=self.sinks, softcap=s.softcap)
+            if gated:
+                ops.gate_into(o, y, cols[3], s.gate, out, out_col, out_scale, s.heads, self.v_dim)
+            elif not direct:
                 ops.scale_into(o, out, out_col, out_scale)
             return
         ops.attention_general(y, cols[0], out, out_col, out_scale, k_pages, v_pages, ctx, cache.block_table, s.heads,
