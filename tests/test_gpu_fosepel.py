@@ -316,6 +316,28 @@ def test_a_token_far_back_still_decides_a_recurrent_state(fosepel_folders, tmp_p
         assert float((got - want).abs().max()) <= cases.tol(dtype, want, alone=name != "parallel_alone")
 
 
+def test_single_tokens_over_many_keys_on_the_tensor_cores(fosepel_folders):
+    """Sinks and capped scores at sizes the tensor-core kernel takes: a prompt of 700 tokens in portions, then single tokens,
+    whose keys are cut into runs with a CTA each (the sink must count in one run only), beside a short request."""
+    from vt_transformer_b200.engine.batch import StepEntry
+    folder = fosepel_folders("tensor")
+    a, b = cases.prompts_for("tensor", seed=4, lengths=[708, 20])
+    runner = cases.runner_for(folder, DEV, "bfloat16", num_pages=48, max_requests=2)
+    ra, rb = runner.admit(), runner.admit()
+    runner.step([StepEntry(ra, a[:450], [])])
+    runner.step([StepEntry(ra, a[450:700], []), StepEntry(rb, b[:12], [])])
+    got_a, got_b = [], []
+    for i in range(8):
+        logits = runner.step([StepEntry(ra, [a[700 + i]], [0]), StepEntry(rb, [b[12 + i]], [0])]).double().cpu()
+        got_a.append(logits[0])
+        got_b.append(logits[1])
+    runner.check_status()
+    for got, ids, first in ((got_a, a, 700), (got_b, b, 12)):
+        ref = _logits(folder, ids)
+        d = (torch.stack(got) - ref[first:first + 8]).abs().max(dim=1).values
+        assert float(d.max()) <= 2 * cases.tol("bfloat16", ref) and int((d > cases.tol("bfloat16", ref)).sum()) <= 1, d
+
+
 @pytest.mark.parametrize("dtype", DTYPES)
 def test_the_state_of_a_row_that_is_used_again_starts_from_zero(fosepel_folders, dtype):
     """A request that leaves a row behind must not hand its state or its convolutions' last inputs to the next request in it."""

@@ -19,7 +19,7 @@ namespace vtb {
 namespace {
 constexpr int kMaxPerLane = 8;       // head sizes up to 256
 constexpr int kWidePerLane = 32;     // values of up to 1,024 numbers for the attention of one map
-constexpr int kPrepareWarps = 4;
+constexpr int kPrepareWarps = 8;
 }
 
 template <typename T>
@@ -69,7 +69,8 @@ attention_prepare_kernel(T* __restrict__ y, int stride, int q_col, int k_col, in
     }
     // the query's temperature: 1 + c ln(floor((p + 1) / n) + 1)
     const float q_times = qt_coef != 0.f ? 1.f + qt_coef * logf((float)((pos + 1) / qt_every) + 1.f) : 1.f;
-    for (int u = warp; u < units; u += kPrepareWarps) {
+    // (a step of few tokens is cut over gridDim.y blocks a token: each takes every gridDim.y-th group of heads)
+    for (int u = warp + kPrepareWarps * blockIdx.y; u < units; u += kPrepareWarps * gridDim.y) {
         const bool is_q = u < heads;
         T* src = is_q ? row + q_col + u * dim : row + k_col + (u - heads) * dim;
         for (int i = lane; i < dim; i += 32) hv[i] = to_float(src[i]);
@@ -122,7 +123,7 @@ attention_prepare_kernel(T* __restrict__ y, int stride, int q_col, int k_col, in
         __syncwarp();
     }
     if (!store) return;
-    for (int e = threadIdx.x; e < v_heads * v_dim; e += blockDim.x) {
+    for (int e = threadIdx.x + blockIdx.y * blockDim.x; e < v_heads * v_dim; e += blockDim.x * gridDim.y) {
         const int h = e / v_dim, i = e % v_dim;
         v_cache[(((size_t)page * v_heads + h) * page_size + slot) * v_dim + i] = row[v_col + e];
     }
@@ -137,12 +138,16 @@ cudaError_t launch_attention_prepare(int dtype, void* y, int stride, int q_col, 
     if (n_tokens == 0) return cudaSuccess;
     if (qt_every < 1) return cudaErrorInvalidValue;
     if (dim > 32 * kMaxPerLane || 2 * half > dim) return cudaErrorInvalidValue;
+    // few tokens: several blocks a token, so that a step of single tokens fills the SMs (not with the norm over the whole
+    // projection: a block would write a head of q back while another still adds up the squares of all of them)
+    const int slices = (n_tokens >= 1024 || whole) ? 1 : max(1, min(8, (heads + kv_heads + 2 * kPrepareWarps - 1) / (2 * kPrepareWarps)));
+    const dim3 grid(n_tokens, slices);
     if (dtype == kBF16)
-        return launch(attention_prepare_kernel<__nv_bfloat16>, n_tokens, 32 * kPrepareWarps, 0, stream, (__nv_bfloat16*)y, stride,
+        return launch(attention_prepare_kernel<__nv_bfloat16>, grid, 32 * kPrepareWarps, 0, stream, (__nv_bfloat16*)y, stride,
                       q_col, k_col, v_col, positions, token_seq, freq, half, norm_eps, (__nv_bfloat16*)k_cache,
                       (__nv_bfloat16*)v_cache, block_table, table_stride, n_seqs, n_pages, heads, kv_heads, dim, v_dim,
                       page_size, store, status, v_heads, q_weight, k_weight, norm_first, whole, rot_mult, qt_coef, qt_every);
-    return launch(attention_prepare_kernel<float>, n_tokens, 32 * kPrepareWarps, 0, stream, (float*)y, stride, q_col, k_col,
+    return launch(attention_prepare_kernel<float>, grid, 32 * kPrepareWarps, 0, stream, (float*)y, stride, q_col, k_col,
                   v_col, positions, token_seq, freq, half, norm_eps, (float*)k_cache, (float*)v_cache, block_table,
                   table_stride, n_seqs, n_pages, heads, kv_heads, dim, v_dim, page_size, store, status, v_heads, q_weight, k_weight,
                   norm_first, whole, rot_mult, qt_coef, qt_every);

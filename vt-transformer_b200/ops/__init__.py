@@ -792,6 +792,10 @@ def tensor_core_attention_takes_extras(dtype, heads: int, kv_heads: int, head_di
             and backend().attention_mma_supports(head_dim, heads, kv_heads, 4))
 
 
+MMA_TARGET_CTAS = 296     # CTAs that a step of single tokens aims at where the mma.sync kernel walks the keys (two for each SM)
+MMA_MAX_SPLITS = 16       # the most runs that a sequence's keys are cut into for that
+
+
 def paged_attention(qkv, out, k_cache, v_cache, ctx, block_table, heads: int, kv_heads: int, head_dim: int,
                     window: Optional[int], scale: float, status=None, chunk: Optional[int] = None, sinks=None,
                     softcap=None) -> torch.Tensor:
@@ -813,13 +817,22 @@ def paged_attention(qkv, out, k_cache, v_cache, ctx, block_table, heads: int, kv
         if not tensor_core_attention_takes_extras(qkv.dtype, heads, kv_heads, head_dim, head_dim, k_cache.shape[2]):
             raise ValueError("paged_attention: sinks and capped scores run on the tensor cores in bfloat16 at head sizes that are "
                              "multiples of 16 up to 128; ops.attention_general takes the others")
+        splits, part_o, part_ml = 1, None, None
         if ctx.max_q_len == 1:
             warps, tiles = 1, None
+            # few sequences leave most SMs without a CTA: every sequence's blocks of 64 keys are cut into equal runs, a CTA
+            # each (the sink counts in the first), merged in the order of the runs
+            blocks = max(1, -(-_key_span(ctx.max_kv_len, w, c) // 64))
+            splits = max(1, min(MMA_MAX_SPLITS, MMA_TARGET_CTAS // max(1, ctx.n_seqs * kv_heads), blocks // 2))
+            if splits > 1:
+                part_o = torch.empty((splits, qkv.shape[0], heads, head_dim), dtype=torch.float32, device=qkv.device)
+                part_ml = torch.empty((splits, qkv.shape[0], heads, 2), dtype=torch.float32, device=qkv.device)
         else:
             warps = 8 if ctx.max_q_len * group >= 128 and be.attention_mma_supports(head_dim, heads, kv_heads, 8) else 4
             tiles = _attention_tiles(ctx, (16 * warps) // group, qkv.device)
         be.attention_mma(qkv, out, k_cache, v_cache, ctx.cu_q, ctx.q_start, block_table, tiles, heads, kv_heads, head_dim, w,
-                         float(scale), warps, 1, None, None, status, chunk=c, sinks=sinks, softcap=float(softcap) if softcap else 0.0)
+                         float(scale), warps, splits, part_o, part_ml, status, chunk=c, sinks=sinks,
+                         softcap=float(softcap) if softcap else 0.0)
         return out
     if qkv.dtype == torch.bfloat16 and ATTENTION_KERNEL in ("auto", "mma"):
         if ctx.max_q_len == 1 and be.attention_mma_supports(head_dim, heads, kv_heads, 1):
