@@ -586,7 +586,7 @@ def design_points(design: str, sizes, steps: int, warmup: int) -> int:
 def main() -> int:
     ap = argparse.ArgumentParser()
     ap.add_argument("--design", default=None, help="instead of the default workload: prefill and decode throughput of this design "
-                    "('sisetar', 'vegilix') at layer sizes that resemble a served model's, beside a Qwen2 model of equal size")
+                    "('sisetar', 'vegilix', 'geponex', 'fosepel') at layer sizes that resemble a served model's, beside a Qwen2 model of equal size")
     ap.add_argument("--design-sizes", default="w1024,w4096", help="which of the sizes of --design to run, with commas between them")
     ap.add_argument("--gpus", type=int, default=1)
     ap.add_argument("--steps", type=int, default=200)

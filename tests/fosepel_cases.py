@@ -85,7 +85,7 @@ CONFIGS: Dict[str, dict] = {
     # sizes of the kind a served model has: heads of 64 and 128, recurrences with keys of 64 and 128 and values of 128
     "tensor": _model(200, 128, [_par2((4, 2, 64, 64, 0.125), (2, 128, 128, 15.0), softcap=30.0, q_temp=(0.2, 128), ff=256),
                                 _att(4, 1, 128, 128, 0.09, rot=_rot(64, 1e4, (4.0, 256, 16.0, 2.0)), ff=96),
-                                _par((4, 4, 64, 32, 0.125), (4, 2, 64, 128, 4), ff=96)], loop=(0, 3, 2), cap=30.0),
+                                _par((4, 2, 64, 64, 0.125), (4, 2, 64, 128, 4), ff=96)], loop=(0, 3, 2), cap=30.0),
 }
 SIGMA = {"mix": 0.15, "wide": 0.12, "attention_alone": 0.25, "parallel_alone": 0.25, "parallel2_alone": 0.25, "dense_alone": 0.2,
          "tensor": 0.1}

@@ -397,3 +397,24 @@ def test_trace_replay_command(fosepel_folders, tmp_path):
     trace = helpers.trace_mixed(prompts, max_live=4, seed=2)
     got = helpers.run_trace_cli(folder, trace, "float32", str(tmp_path / "out"), helpers.tokens_needed(trace, 64))
     cases.compare(folder, prompts, trace, got, "float32")
+
+
+def test_generate_from_the_command_line_greedy(fosepel_folders):
+    import os
+    import subprocess
+    import sys
+    folder = fosepel_folders("wide")
+    prompts = cases.prompts_for("wide")[:2]
+    base = [sys.executable, "-m", "vt_transformer_b200", "generate", "--model", folder, "--dtype", "float32", "--max-tokens", "6",
+            "--ignore-eos", "--num-pages", "16", "--max-seq-len", "128", "--page-size", "16", "--temperature", "0"]
+    for p in prompts:
+        base += ["--prompt-ids", ",".join(str(t) for t in p)]
+    res = subprocess.run(base, capture_output=True, text=True, timeout=600, env=dict(os.environ, PYTHONPATH=helpers.ROOT), cwd=helpers.ROOT)
+    assert res.returncode == 0, res.stderr[-3000:]
+    lines = [[int(t) for t in l.split()] for l in res.stdout.splitlines() if l.strip()]
+    assert len(lines) == 2 and all(len(l) == 6 for l in lines)
+    for p, o in zip(prompts, lines):
+        ref = _logits(folder, list(p) + o)
+        for i, tok in enumerate(o):
+            row = ref[len(p) - 1 + i]
+            assert float(row.max() - row[tok]) <= 2 * cases.tol("float32", ref)

@@ -59,6 +59,7 @@ struct AttnTcParams {
     int run_keys;            // keys of a run: 16, 32, 64 or 128, a divisor of the page size
     int cache_rows;          // pages * kv_heads * page_size: a row index beyond it makes TMA fill zeros
     int* status;
+    const float* sinks;      // [heads] or null: one more term exp(sinks[head]) in a row's denominator, without a key or a value
 };
 
 __device__ __forceinline__ float ex2(float x) {
@@ -321,6 +322,12 @@ attention_tc_kernel(const __grid_constant__ CUtensorMap map_k, const __grid_cons
         const uint32_t s_addr = tmem + lane_base + (uint32_t)(g * TK);
         const uint32_t o_addr = tmem + lane_base + (uint32_t)(2 * TK + g * D);
         float m = -INFINITY, l = 0.f;       // the maximum P is scaled by (in log2 units), and the sum at that scale
+        if (p.sinks != nullptr && g == 0 && valid) {
+            // the sink is a first key without a value, in the group of the even blocks: its score is the scale to begin
+            // with and it counts once in the sum
+            m = p.sinks[head] * 1.4426950408889634f;
+            l = 1.f;
+        }
         for (int j = g; j < nb && !timed_out; j += 2) {
             const int u = j >> 1;           // the group's u-th block
             if (!mbar_wait(&s_full[g], u & 1)) { timed_out = true; break; }
@@ -337,7 +344,13 @@ attention_tc_kernel(const __grid_constant__ CUtensorMap map_k, const __grid_cons
             const float mx = fmaxf(m, raw_max * p.scale_log2);          // the scale is positive
             // a row that has seen no key yet takes the maximum as it is: its O is still zero
             const bool raise = (m != -INFINITY) && (mx > m + RAISE);
-            if (__any_sync(0xffffffffu, raise)) {
+            if (u == 0) {
+                // before the group's first block O holds nothing: a scale that only the sink has set moves without it
+                if (raise) {
+                    l *= ex2(m - mx);
+                    m = mx;
+                }
+            } else if (__any_sync(0xffffffffu, raise)) {
                 // O of this group, as the product of its block before left it, times 2^(old - new maximum)
                 if (!mbar_wait(&o_done[g], (u - 1) & 1)) { timed_out = true; break; }
                 tc_fence_after();
@@ -450,7 +463,8 @@ bool attention_tc_supports(int head_dim, int heads, int kv_heads) {
 cudaError_t launch_attention_tc(const void* qkv, int qkv_stride, void* out, const void* k_cache, const void* v_cache,
                                 const int* cu_q, const int* q_start, const int* block_table, int table_stride,
                                 const int* tiles, int n_tiles, int n_pages, int heads, int kv_heads, int head_dim,
-                                int page_size, int window, float scale, int* status, cudaStream_t stream, int chunk) {
+                                int page_size, int window, float scale, int* status, cudaStream_t stream, int chunk,
+                                const float* sinks) {
     if (n_tiles == 0) return cudaSuccess;
     if (!attention_tc_supports(head_dim, heads, kv_heads) || page_size % 16 != 0 || tiles == nullptr) return cudaErrorInvalidValue;
     const long long cache_rows = (long long)n_pages * kv_heads * page_size;
@@ -479,6 +493,7 @@ cudaError_t launch_attention_tc(const void* qkv, int qkv_stride, void* out, cons
     p.cache_rows = (int)cache_rows;
     p.run_keys = run_keys;
     p.status = status;
+    p.sinks = sinks;
     // Q, two stages of K and of V (HALVES halves of 16 KB each), barriers, the exchange; never so little that two CTAs
     // would fit an SM: each takes all of its tensor memory
     const int halves = head_dim / 64;

@@ -1044,7 +1044,7 @@ bool attention_tc_supports(int64_t head_dim, int64_t heads, int64_t kv_heads) {
 
 void attention_tc(const Tensor& qkv, Tensor& out, const Tensor& k_cache, const Tensor& v_cache, const Tensor& cu_q,
                   const Tensor& q_start, const Tensor& block_table, const Tensor& tiles, int64_t heads, int64_t kv_heads,
-                  int64_t head_dim, int64_t window, double scale, c10::optional<Tensor> status, int64_t chunk) {
+                  int64_t head_dim, int64_t window, double scale, c10::optional<Tensor> status, int64_t chunk, c10::optional<Tensor> sinks) {
     check_cuda(qkv, "qkv"); check_cuda(out, "out"); check_i32(cu_q, "cu_q"); check_i32(q_start, "q_start");
     check_i32(block_table, "block_table"); check_i32(tiles, "tiles");
     TORCH_CHECK(qkv.scalar_type() == torch::kBFloat16 && out.scalar_type() == torch::kBFloat16,
@@ -1066,12 +1066,18 @@ void attention_tc(const Tensor& qkv, Tensor& out, const Tensor& k_cache, const T
     TORCH_CHECK(q_start.numel() == n_seqs && block_table.dim() == 2 && block_table.size(0) == n_seqs,
                 "attention_tc: one q_start and one block-table row for each sequence");
     TORCH_CHECK(tiles.dim() == 2 && tiles.size(1) == 2, "attention_tc: tiles must be [n, 2]");
+    const float* sinks_tc = nullptr;
+    if (sinks.has_value()) {
+        check_f32(*sinks, "sinks");
+        TORCH_CHECK(sinks->numel() == heads, "attention_tc: one sink a head");
+        sinks_tc = sinks->data_ptr<float>();
+    }
     c10::cuda::CUDAGuard guard(qkv.device());
     check_launch(vtb::launch_attention_tc(qkv.data_ptr(), qkv.size(1), out.data_ptr(), k_cache.data_ptr(),
                                           v_cache.data_ptr(), cu_q.data_ptr<int>(), q_start.data_ptr<int>(),
                                           block_table.data_ptr<int>(), block_table.size(1), tiles.data_ptr<int>(),
                                           tiles.size(0), k_cache.size(0), heads, kv_heads, head_dim, k_cache.size(2),
-                                          window, (float)scale, status_ptr(status), stream_of(qkv), (int)chunk),
+                                          window, (float)scale, status_ptr(status), stream_of(qkv), (int)chunk, sinks_tc),
                  "attention_tc");
 }
 
@@ -1286,7 +1292,7 @@ PYBIND11_MODULE(TORCH_EXTENSION_NAME, m) {
     m.def("attention_tc", &attention_tc, py::arg("qkv"), py::arg("out"), py::arg("k_cache"), py::arg("v_cache"),
           py::arg("cu_q"), py::arg("q_start"), py::arg("block_table"), py::arg("tiles"), py::arg("heads"),
           py::arg("kv_heads"), py::arg("head_dim"), py::arg("window"), py::arg("scale"), py::arg("status") = py::none(),
-          py::arg("chunk") = 0);
+          py::arg("chunk") = 0, py::arg("sinks") = py::none());
     m.def("attention_decode", &attention_decode, py::arg("qkv"), py::arg("out"), py::arg("k_cache"), py::arg("v_cache"),
           py::arg("cu_q"), py::arg("q_start"), py::arg("block_table"), py::arg("heads"), py::arg("kv_heads"),
           py::arg("head_dim"), py::arg("window"), py::arg("scale"), py::arg("n_splits"), py::arg("part_o") = py::none(),

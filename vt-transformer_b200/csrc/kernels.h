@@ -293,7 +293,8 @@ bool attention_tc_supports(int head_dim, int heads, int kv_heads);
 cudaError_t launch_attention_tc(const void* qkv, int qkv_stride, void* out, const void* k_cache, const void* v_cache,
                                 const int* cu_q, const int* q_start, const int* block_table, int table_stride,
                                 const int* tiles, int n_tiles, int n_pages, int heads, int kv_heads, int head_dim,
-                                int page_size, int window, float scale, int* status, cudaStream_t stream, int chunk = 0);
+                                int page_size, int window, float scale, int* status, cudaStream_t stream, int chunk = 0,
+                                const float* sinks = nullptr);
 
 // Attention of single-token steps: every sequence brings tokens_per_tile = 16 / group tokens at most (one in a
 // decode step).  Grid (sequences, kv_heads, n_splits), four warps a CTA.  With n_splits > 1 the runs' results

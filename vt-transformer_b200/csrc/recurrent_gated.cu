@@ -7,7 +7,7 @@
 //   matrix memory  m' = max(f_t + m, i_t);  S <- exp(f_t + m - m') S + exp(i_t - m') k_t v_t^T;  n likewise with k_t alone;
 //                  o_t = S^T q_t / (max(|n . q_t|, exp(-m')) + eps)
 // Column j of S depends on column j alone: a warp owns 32 columns of one (sequence, head), a thread keeps KD rows of its
-// column in registers (16), and G = dim / 16 threads share a column (their partial sums meet in shared memory, in the
+// column in registers (8), and G = dim / 8 threads share a column (their partial sums meet in shared memory, in the
 // order of g).  The step's tokens of the sequence are staged 16 at a time: the convolutions and their silu, the unit
 // vectors, the gates, the running maximum and the normalizer are formed once for all columns, in 32-bit; then the
 // warps walk the batch out of shared memory.  A decoded token is a walk of one token.  The order of every sum depends
@@ -21,12 +21,13 @@ namespace vtb {
 namespace {
 
 constexpr int kCols = 32;        // columns of the state a warp owns
-constexpr int kTokens = 16;      // tokens staged at once
-constexpr int kRows = 16;        // rows of its column that a thread keeps in registers
+constexpr int kTokens = 16;      // tokens staged at once in steps of single tokens and short portions
+constexpr int kWalkTokens = 32;  // ... and in long walks, where the staging's fixed waits weigh more
+constexpr int kRows = 8;         // rows of its column that a thread keeps in registers
 constexpr int kMaxThreads = 1024;
 // Threads of a CTA in a step that is a long walk of few sequences: a head's column blocks then spread over several SMs
 // (each forms the gates again); steps of single tokens keep as many of a head's columns in one CTA as fit.
-constexpr int kWalkThreads = 256;
+constexpr int kWalkThreads = 512;
 
 struct GatedArgs {
     const void* y;               // [tokens, stride]: the projections
@@ -62,14 +63,14 @@ __device__ __forceinline__ float log_sigmoid_f(float z) { return z < 0.f ? z - l
 // blockIdx.z * CB * 32 + cb * 32 + c.
 // WALK: the variant for long walks of few sequences, compiled for CTAs of 256 threads (and the registers they may have).
 template <typename T, int KD, int MODE, bool WALK>
-__global__ void __launch_bounds__(WALK ? kWalkThreads : kMaxThreads)
+__global__ void __launch_bounds__(WALK ? kWalkThreads : kMaxThreads, 1)
 gated_scan_kernel(const GatedArgs a) {
     extern __shared__ __align__(16) float smem[];
     pdl_launch();
     const int seq = blockIdx.x, h = blockIdx.y;
     const int c = threadIdx.x, g = threadIdx.y, cb = threadIdx.z;
     const int G = a.groups, CB = a.col_blocks;
-    constexpr int TB = kTokens;
+    constexpr int TB = WALK ? kWalkTokens : kTokens;
     const int tid = (cb * G + g) * kCols + c, n_threads = kCols * G * CB;
     const int warp = tid >> 5, n_warps = n_threads >> 5;
     const int dim = a.dim, v_dim = a.v_dim;
@@ -345,11 +346,12 @@ cudaError_t launch_gated_kd(const GatedArgs& a, int n_seqs, int most_threads, cu
     args.col_blocks = cb;
     const int dim_p = G * KD, cols = cb * kCols, per = 2 * dim_p + cols;
     const int taps = MODE == 0 ? a.taps : 1;
-    size_t floats = (size_t)2 * kTokens * dim_p + kTokens * cols + kTokens * 4 + 2 * cb * G * kCols + (size_t)kTokens * G * cols;
-    floats += MODE == 0 ? (size_t)(kTokens + taps - 1) * per + (size_t)taps * per : (size_t)kTokens * dim_p + 4;
+    const bool walk = most_threads > 0 && cb * kCols * G <= kWalkThreads;
+    const int tb = walk ? kWalkTokens : kTokens;
+    size_t floats = (size_t)2 * tb * dim_p + tb * cols + tb * 4 + 2 * cb * G * kCols + (size_t)tb * G * cols;
+    floats += MODE == 0 ? (size_t)(tb + taps - 1) * per + (size_t)taps * per : (size_t)tb * dim_p + 4;
     const size_t bytes = floats * sizeof(float);
     if (bytes > 200 * 1024) return cudaErrorInvalidValue;
-    const bool walk = most_threads > 0 && cb * kCols * G <= kWalkThreads;
     auto kernel = walk ? gated_scan_kernel<T, KD, MODE, true> : gated_scan_kernel<T, KD, MODE, false>;
     static std::atomic<unsigned long long> done[2] = {{0}, {0}};
     if (cudaError_t e = allow_dynamic_smem(kernel, 200 * 1024, done[walk ? 1 : 0]); e != cudaSuccess) return e;
@@ -368,9 +370,11 @@ cudaError_t launch_gated_kd(const GatedArgs& a, int n_seqs, int most_threads, cu
 
 template <typename T, int MODE>
 cudaError_t launch_gated_t(const GatedArgs& a, int n_seqs, int most_threads, cudaStream_t stream) {
-    // 16 rows a thread: the G = dim / 16 warps of a column block work side by side and meet only where the recurrence needs
+    // 8 rows a thread: the G = dim / 8 warps of a column block work side by side and meet only where the recurrence needs
     // the whole column (the delta rule's S^T k, once a token)
-    return launch_gated_kd<T, kRows, MODE>(a, n_seqs, most_threads > 0 ? kWalkThreads : 0, stream);
+    // (measured on a B200 at 16 heads of 128 x 256, 2,048 tokens: 16 rows a thread 2.8 / 1.8 ms (delta rule / matrix memory),
+    // 8 rows 2.0 / 1.15 ms, 4 rows 2.9 / 1.13 ms: more warps hide the chain of multiply-adds, until the meeting of 32 warps costs more)
+    return launch_gated_kd<T, kRows, MODE>(a, n_seqs, most_threads > 0 ? 256 : 0, stream);
 }
 
 }  // namespace

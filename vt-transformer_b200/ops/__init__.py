@@ -817,6 +817,14 @@ def paged_attention(qkv, out, k_cache, v_cache, ctx, block_table, heads: int, kv
         if not tensor_core_attention_takes_extras(qkv.dtype, heads, kv_heads, head_dim, head_dim, k_cache.shape[2]):
             raise ValueError("paged_attention: sinks and capped scores run on the tensor cores in bfloat16 at head sizes that are "
                              "multiples of 16 up to 128; ops.attention_general takes the others")
+        if (not softcap and ATTENTION_KERNEL == "auto" and ctx.max_q_len * group >= 128 and k_cache.shape[2] % 16 == 0
+                and be.attention_tc_supports(head_dim, heads, kv_heads)):
+            # portions long enough to fill tiles of 128 rows, a sink and no cap: the tcgen05 kernel (the sink is the start
+            # of a row's scale and sum there too)
+            tiles = _attention_tiles(ctx, 128 // group, qkv.device)
+            be.attention_tc(qkv, out, k_cache, v_cache, ctx.cu_q, ctx.q_start, block_table, tiles, heads, kv_heads, head_dim, w,
+                            float(scale), status, chunk=c, sinks=sinks)
+            return out
         splits, part_o, part_ml = 1, None, None
         if ctx.max_q_len == 1:
             warps, tiles = 1, None
