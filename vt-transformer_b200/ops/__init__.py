@@ -794,6 +794,7 @@ def tensor_core_attention_takes_extras(dtype, heads: int, kv_heads: int, head_di
 
 MMA_TARGET_CTAS = 296     # CTAs that a step of single tokens aims at where the mma.sync kernel walks the keys (two for each SM)
 MMA_MAX_SPLITS = 16       # the most runs that a sequence's keys are cut into for that
+MMA_SINGLE_TOKEN_WARPS = int(os.environ.get("VTB200_MMA_SINGLE_TOKEN_WARPS", "4"))
 
 
 def paged_attention(qkv, out, k_cache, v_cache, ctx, block_table, heads: int, kv_heads: int, head_dim: int,
@@ -827,7 +828,8 @@ def paged_attention(qkv, out, k_cache, v_cache, ctx, block_table, heads: int, kv
             return out
         splits, part_o, part_ml = 1, None, None
         if ctx.max_q_len == 1:
-            warps, tiles = 1, None
+            # (a tile a sequence; four warps bring a block of keys four times as fast as one, though one holds all its rows)
+            warps, tiles = MMA_SINGLE_TOKEN_WARPS if be.attention_mma_supports(head_dim, heads, kv_heads, MMA_SINGLE_TOKEN_WARPS) else 1, None
             # few sequences leave most SMs without a CTA: every sequence's blocks of 64 keys are cut into equal runs, a CTA
             # each (the sink counts in the first), merged in the order of the runs
             blocks = max(1, -(-_key_span(ctx.max_kv_len, w, c) // 64))
