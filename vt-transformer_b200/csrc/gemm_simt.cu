@@ -3,9 +3,10 @@
 //
 // vt-transformer sends its 32-bit products to cuBLASLt and lets it pick tensor operations
 // (v1/tensortype/cuda_kernels/lt_sgemm.cu:53-54), so it has no verified 32-bit run.  With float
-// operands this kernel is the engine's 32-bit path: every output element is the sum over
-// k = 0, 1, 2, ... in that order, whatever M is and whatever else is in the batch, so logits
-// agree bit for bit however the tokens are cut into steps.  With bfloat16 operands it is the
+// operands this kernel is the engine's 32-bit path: every output element is the sum, over the
+// runs of 16 consecutive k in their order, of each run's sum over its k in their order (two
+// levels: the rounding error grows with 16 + K / 16 terms, not with K), whatever M is and whatever
+// else is in the batch, so logits agree bit for bit however the tokens are cut into steps.  With bfloat16 operands it is the
 // plain twin of the tensor-core products.
 #include "common.cuh"
 #include "kernels.h"
@@ -53,6 +54,7 @@ gemm_simt_kernel(const TA* __restrict__ a, const TA* __restrict__ w, const float
         as[lk + 0][lrow] = av.x; as[lk + 1][lrow] = av.y; as[lk + 2][lrow] = av.z; as[lk + 3][lrow] = av.w;
         ws[lk + 0][lrow] = wv.x; ws[lk + 1][lrow] = wv.y; ws[lk + 2][lrow] = wv.z; ws[lk + 3][lrow] = wv.w;
         __syncthreads();
+        float part[4][4] = {};                       // this run of k alone
 #pragma unroll
         for (int kk = 0; kk < BK; ++kk) {
             const float4 x = *reinterpret_cast<const float4*>(&as[kk][ty * 4]);
@@ -61,8 +63,12 @@ gemm_simt_kernel(const TA* __restrict__ a, const TA* __restrict__ w, const float
 #pragma unroll
             for (int i = 0; i < 4; ++i)
 #pragma unroll
-                for (int j = 0; j < 4; ++j) acc[i][j] = fmaf(xs[i], ys[j], acc[i][j]);
+                for (int j = 0; j < 4; ++j) part[i][j] = fmaf(xs[i], ys[j], part[i][j]);
         }
+#pragma unroll
+        for (int i = 0; i < 4; ++i)
+#pragma unroll
+            for (int j = 0; j < 4; ++j) acc[i][j] += part[i][j];
         __syncthreads();
     }
 #pragma unroll
